@@ -1,0 +1,286 @@
+// C interface (include/fp6_llm_b200.h) and the C++ interface with the reference's names
+// (include/fp6_llm_b200_cxx.cuh) of libfp6_b200.so.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <mutex>
+
+#include "../../include/fp6_llm_b200.h"
+#include "../../include/fp6_llm_b200_cxx.cuh"
+#include "fpx_internal.h"
+
+namespace {
+
+// First time-out code recorded by a GEMM CTA (0 = none); one word per device that loads the library.
+__device__ int g_gemm_status = 0;
+
+constexpr int kMaxDevices = 64;
+
+int* status_ptr() {
+    static int* ptrs[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_gemm_status) != cudaSuccess) return nullptr;
+        ptrs[dev] = static_cast<int*>(p);
+    }
+    return ptrs[dev];
+}
+
+int sm_count() {
+    static int counts[kMaxDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    if (!counts[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        counts[dev] = n;
+    }
+    return counts[dev];
+}
+
+// Grow-only device staging buffer for the *_host entry points (one per device, calls are serialised).
+struct Staging {
+    std::mutex mu;
+    void* buf[kMaxDevices] = {};
+    size_t cap[kMaxDevices] = {};
+    cudaStream_t stream[kMaxDevices] = {};
+};
+Staging& staging() {
+    static Staging s;
+    return s;
+}
+cudaError_t staging_get(size_t bytes, void** out, cudaStream_t* stream) {
+    Staging& s = staging();
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!s.stream[dev]) {
+        err = cudaStreamCreateWithFlags(&s.stream[dev], cudaStreamNonBlocking);
+        if (err != cudaSuccess) return err;
+    }
+    if (s.cap[dev] < bytes) {
+        if (s.buf[dev]) cudaFree(s.buf[dev]);
+        s.buf[dev] = nullptr;
+        s.cap[dev] = 0;
+        const size_t want = bytes + bytes / 4;
+        err = cudaMalloc(&s.buf[dev], want);
+        if (err != cudaSuccess) return err;
+        s.cap[dev] = want;
+    }
+    *out = s.buf[dev];
+    *stream = s.stream[dev];
+    return cudaSuccess;
+}
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int choose_split_k(size_t M, size_t N, size_t K, int num_sms) {
+    if (M == 0 || N == 0 || K < 64 || num_sms <= 0) return 1;
+    const int n_tile = fpx::gemm_n_tile(N);
+    const double slots = (double)num_sms * fpx::gemm_ctas_per_sm(n_tile);
+    const double tiles = (double)(M / 128) * (double)((N + n_tile - 1) / n_tile);
+    const size_t kblocks = K / 64;
+    // Cost in units of "one 64-wide K block of one CTA": every CTA pays a fixed start-up/epilogue
+    // cost, a split adds a second kernel plus the fp32 partial round trip.
+    const double cta_overhead = 10.0;
+    const double reduce_launch = 12.0;
+    int best = 1;
+    double best_cost = 1e300;
+    const size_t max_split = kblocks < 32 ? kblocks : 32;
+    for (size_t k = 1; k <= max_split; k++) {
+        const double waves = ceil(tiles * (double)k / slots);
+        const double per_cta = ceil((double)kblocks / (double)k) + cta_overhead;
+        // partial traffic: k*M*N*4 bytes written and read, versus 128*64*0.75 bytes per K block unit
+        const double partial = k > 1 ? reduce_launch + 2.0 * (double)k * (double)M * (double)N * 4.0 / (6144.0 * slots) : 0.0;
+        const double cost = waves * per_cta + partial;
+        if (cost < best_cost * 0.97) {   // prefer the smaller split unless the gain is clear
+            best_cost = cost;
+            best = (int)k;
+        }
+    }
+    return best;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp6b200_version(void) { return 1; }
+
+const char* fp6b200_error_string(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }
+
+int fp6b200_choose_split_k(size_t M, size_t N, size_t K, int num_sms) { return choose_split_k(M, N, K, num_sms); }
+
+size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k) {
+    if (split_k == 0) split_k = choose_split_k(M, N, K, sm_count());
+    return split_k > 1 ? (size_t)split_k * M * N * sizeof(float) : 0;
+}
+
+int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,
+                   const void* act, void* out, size_t M, size_t N, size_t K, float* workspace, int split_k) {
+    if (split_k == 0) split_k = choose_split_k(M, N, K, sm_count());
+    int* status = status_ptr();
+    if (!status) return cudaErrorInitializationError;
+    return fpx::launch_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_packed,
+                            static_cast<const __half*>(scales), static_cast<const __half*>(act),
+                            static_cast<__half*>(out), M, N, K, workspace, split_k, status);
+}
+
+int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev, const void* scales_dev,
+                           const void* act_host, void* out_host, size_t M, size_t N, size_t K, int split_k) {
+    if (!act_host || !out_host) return cudaErrorInvalidValue;
+    if (split_k == 0) split_k = choose_split_k(M, N, K, sm_count());
+    if (split_k < 1) return cudaErrorInvalidValue;
+    const size_t act_bytes = align_up(N * K * sizeof(__half), 256), out_bytes = align_up(N * M * sizeof(__half), 256);
+    const size_t ws_bytes = split_k > 1 ? (size_t)split_k * M * N * sizeof(float) : 0;
+    std::lock_guard<std::mutex> lock(staging().mu);
+    void* base = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaError_t err = staging_get(act_bytes + out_bytes + ws_bytes, &base, &stream);
+    if (err != cudaSuccess) return err;
+    char* p = static_cast<char*>(base);
+    __half* act = reinterpret_cast<__half*>(p);
+    __half* out = reinterpret_cast<__half*>(p + act_bytes);
+    float* ws = ws_bytes ? reinterpret_cast<float*>(p + act_bytes + out_bytes) : nullptr;
+    err = cudaMemcpyAsync(act, act_host, N * K * sizeof(__half), cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) return err;
+    int* status = status_ptr();
+    if (!status) return cudaErrorInitializationError;
+    err = fpx::launch_gemm(e_bits, m_bits, stream, weight_packed_dev, static_cast<const __half*>(scales_dev), act, out,
+                           M, N, K, ws, split_k, status);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(out_host, out, N * M * sizeof(__half), cudaMemcpyDeviceToHost, stream);
+    if (err != cudaSuccess) return err;
+    return cudaStreamSynchronize(stream);
+}
+
+int fp6b200_prepack(int e_bits, int m_bits, void* stream, const void* unpacked_dev, void* packed_dev, size_t M,
+                    size_t K) {
+    return fpx::launch_prepack(e_bits, m_bits, static_cast<cudaStream_t>(stream), unpacked_dev, packed_dev, M, K);
+}
+
+int fp6b200_prepack_host(int e_bits, int m_bits, int* packed_host, const int* unpacked_host, size_t M, size_t K) {
+    if (!fpx::format_supported(e_bits, m_bits) || !packed_host || !unpacked_host || M % 64 || K % 64 || !M || !K)
+        return cudaErrorInvalidValue;
+    const size_t bytes = M * K * (size_t)(1 + e_bits + m_bits) / 8, padded = align_up(bytes, 256);
+    std::lock_guard<std::mutex> lock(staging().mu);
+    void* base = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaError_t err = staging_get(2 * padded, &base, &stream);
+    if (err != cudaSuccess) return err;
+    char* in = static_cast<char*>(base);
+    char* out = in + padded;
+    err = cudaMemcpyAsync(in, unpacked_host, bytes, cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) return err;
+    err = fpx::launch_prepack(e_bits, m_bits, stream, in, out, M, K);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(packed_host, out, bytes, cudaMemcpyDeviceToHost, stream);
+    if (err != cudaSuccess) return err;
+    return cudaStreamSynchronize(stream);
+}
+
+int fp6b200_dequant(int e_bits, int m_bits, void* stream, const void* unpacked_dev, const void* scales_dev,
+                    void* out_dev, size_t M, size_t K) {
+    return fpx::launch_dequant_unpacked(e_bits, m_bits, static_cast<cudaStream_t>(stream), unpacked_dev,
+                                        static_cast<const __half*>(scales_dev), static_cast<__half*>(out_dev), M, K);
+}
+
+int fp6b200_dequant_host(int e_bits, int m_bits, void* out_host, const void* unpacked_host, size_t M, size_t K,
+                         const void* scales_host) {
+    if (!fpx::format_supported(e_bits, m_bits) || !out_host || !unpacked_host || !scales_host || M % 64 || K % 64 ||
+        !M || !K)
+        return cudaErrorInvalidValue;
+    const size_t in_bytes = M * K * (size_t)(1 + e_bits + m_bits) / 8, in_pad = align_up(in_bytes, 256);
+    const size_t sc_pad = align_up(M * sizeof(__half), 256), out_bytes = M * K * sizeof(__half);
+    std::lock_guard<std::mutex> lock(staging().mu);
+    void* base = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaError_t err = staging_get(in_pad + sc_pad + out_bytes, &base, &stream);
+    if (err != cudaSuccess) return err;
+    char* in = static_cast<char*>(base);
+    __half* sc = reinterpret_cast<__half*>(in + in_pad);
+    __half* out = reinterpret_cast<__half*>(in + in_pad + sc_pad);
+    err = cudaMemcpyAsync(in, unpacked_host, in_bytes, cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(sc, scales_host, M * sizeof(__half), cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) return err;
+    err = fpx::launch_dequant_unpacked(e_bits, m_bits, stream, in, sc, out, M, K);
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyAsync(out_host, out, out_bytes, cudaMemcpyDeviceToHost, stream);
+    if (err != cudaSuccess) return err;
+    return cudaStreamSynchronize(stream);
+}
+
+int fp6b200_dequant_packed(int e_bits, int m_bits, void* stream, const void* packed_dev, const void* scales_dev,
+                           void* out_dev, size_t M, size_t K) {
+    return fpx::launch_dequant_packed(e_bits, m_bits, static_cast<cudaStream_t>(stream), packed_dev,
+                                      static_cast<const __half*>(scales_dev), static_cast<__half*>(out_dev), M, K);
+}
+
+int fp6b200_splitk_reduce(void* stream, void* out_dev, const float* partials_dev, size_t elems, int split_k) {
+    if (!out_dev || !partials_dev || elems == 0 || elems % 4 || split_k < 1) return cudaErrorInvalidValue;
+    return fpx::launch_splitk_reduce(static_cast<cudaStream_t>(stream), static_cast<__half*>(out_dev), partials_dev,
+                                     elems, split_k);
+}
+
+int fp6b200_device_status(int* code) {
+    if (!code) return cudaErrorInvalidValue;
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err != cudaSuccess) return err;
+    err = cudaMemcpyFromSymbol(code, g_gemm_status, sizeof(int));
+    if (err != cudaSuccess) return err;
+    if (*code != 0) {
+        const int zero = 0;
+        err = cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+    }
+    return err;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ C++ names of the reference
+cudaError_t fp6_linear_kernel(cudaStream_t stream, const uint4* Weight, const half* Scales, const half* B, half* C,
+                              const size_t M_Global, const size_t N_Global, const size_t K_Global,
+                              float* Reduction_Workspace, int Split_K) {
+    return static_cast<cudaError_t>(
+        fp6b200_linear(3, 2, stream, Weight, Scales, B, C, M_Global, N_Global, K_Global, Reduction_Workspace, Split_K));
+}
+
+cudaError_t fp_eXmY_linear_kernel(const int EXPONENT, const int MANTISSA, cudaStream_t stream, const uint4* Weight,
+                                  const half* Scales, const half* B, half* C, const size_t M_Global,
+                                  const size_t N_Global, const size_t K_Global, float* Reduction_Workspace,
+                                  int Split_K) {
+    return static_cast<cudaError_t>(fp6b200_linear(EXPONENT, MANTISSA, stream, Weight, Scales, B, C, M_Global, N_Global,
+                                                   K_Global, Reduction_Workspace, Split_K));
+}
+
+void weight_matrix_prepacking_fp_eXmY(const int EXPONENT, const int MANTISSA, int* packed_weights, int* FPxWeights,
+                                      size_t M, size_t K) {
+    const int rc = fp6b200_prepack_host(EXPONENT, MANTISSA, packed_weights, FPxWeights, M, K);
+    if (rc != 0)
+        fprintf(stderr, "fp6_llm_b200: weight prepacking failed (e%dm%d, %zux%zu): %s\n", EXPONENT, MANTISSA, M, K,
+                fp6b200_error_string(rc));
+}
+
+void weight_matrix_prepacking(int* packed_weights, int* FP6Weights, size_t M, size_t K) {
+    weight_matrix_prepacking_fp_eXmY(3, 2, packed_weights, FP6Weights, M, K);
+}
+
+void dequant_matrix_fp_eXmY_to_fp16(const int EXPONENT, const int MANTISSA, half* A_16bit_h, unsigned char* A_6bit_h,
+                                    size_t M, size_t K, half* scale) {
+    const int rc = fp6b200_dequant_host(EXPONENT, MANTISSA, A_16bit_h, A_6bit_h, M, K, scale);
+    if (rc != 0)
+        fprintf(stderr, "fp6_llm_b200: weight dequantisation failed (e%dm%d, %zux%zu): %s\n", EXPONENT, MANTISSA, M, K,
+                fp6b200_error_string(rc));
+}
+
+void DeQuantMatrix_FP6_To_FP16(half* A_16bit_h, unsigned char* A_6bit_h, size_t M, size_t K, half* scale) {
+    dequant_matrix_fp_eXmY_to_fp16(3, 2, A_16bit_h, A_6bit_h, M, K, scale);
+}

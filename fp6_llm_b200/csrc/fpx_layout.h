@@ -1,0 +1,164 @@
+// Index arithmetic and bit manipulation of the FPx prepacked weight format, shared by the
+// device kernels and by a host-compiled test harness (everything here is integer-only and
+// host/device callable).
+//
+// The format is the one produced by the reference packer
+// (fp6_llm/csrc/utils/weight_prepacking.h:118-196) and consumed by its GPU dequantiser
+// (fp6_llm/csrc/include/utils_parallel_dequant.cuh:44-99):
+//   * a bw-bit code [sign | E exponent bits | M mantissa bits] is cut, MSB first, into a 1-bit,
+//     a 2-bit and a 4-bit segment (a segment exists iff that bit of bw is set);
+//   * the packed buffer is [1-bit region][2-bit region][4-bit region] over the whole matrix;
+//   * inside a region the unit is a 32-bit word owned by one of 32 "lanes"; lane 4g+t owns, in
+//     every 16x16 block, rows {g, g+8} x cols {2t, 2t+1, 2t+8, 2t+9} (8 codes);
+//   * blocks are ordered (64-row block i, 16-col block j, 16-row sub-block k); a word holds the
+//     segments of 32/w codes, i.e. of 4/w... consecutive blocks, bit-interleaved so that masking
+//     the top w bits of every byte and then shifting left by w walks the codes in use order.
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define FPX_HD __host__ __device__ __forceinline__
+#else
+#define FPX_HD inline
+#endif
+
+namespace fpx {
+
+constexpr int kRowsPerBlock = 64;   // rows whose data is contiguous along K in every region
+constexpr int kKBlock = 64;         // K extent of one pipeline stage (4 column blocks of 16)
+
+FPX_HD constexpr int bit_width(int e_bits, int m_bits) { return 1 + e_bits + m_bits; }
+FPX_HD constexpr bool has_seg(int bw, int w) { return (bw & w) != 0; }
+
+// Byte offset of the region that stores the w-bit segments (w in {1,2,4}).
+FPX_HD uint64_t region_offset(int bw, int w, uint64_t rows, uint64_t cols) {
+    uint64_t off = 0;
+    if (w > 1 && has_seg(bw, 1)) off += rows * cols / 8;
+    if (w > 2 && has_seg(bw, 2)) off += rows * cols / 4;
+    return off;
+}
+
+// Bytes of one (64-row block x 64-K block) tile in the w-bit region: 64*64*w/8.
+FPX_HD constexpr uint32_t tile_bytes(int w) { return 512u * (uint32_t)w; }
+
+// Number of low bits of the code that lie below the w-bit segment.
+FPX_HD constexpr int seg_shift(int bw, int w) {
+    // segments are taken MSB first in the order 1, 2, 4
+    return w == 4 ? 0 : (w == 2 ? (has_seg(bw, 4) ? 4 : 0) : ((has_seg(bw, 2) ? 2 : 0) + (has_seg(bw, 4) ? 4 : 0)));
+}
+
+struct FieldSource {
+    uint32_t row;   // absolute row of the code
+    uint32_t col;   // absolute column of the code
+};
+
+// For the 32-bit word `word_in_lane` of lane `lane` in the w-bit region, the code whose
+// segment sits in field p (field p occupies bits [32-(p+1)w, 32-pw) of the little-endian word).
+FPX_HD FieldSource field_source(int w, uint64_t word_in_lane, int lane, int p, uint32_t cols) {
+    const int fields_per_byte = 8 / w;
+    const int byteidx = p / fields_per_byte;       // byte of the word, counted from the MSB
+    const int n = p % fields_per_byte;             // dequant iteration that consumes this field
+    // the dequantiser reads codes (4n+1, 4n+3, 4n, 4n+2) from the bytes (MSB .. LSB) of iteration n
+    const int q = (byteidx == 0) ? 1 : (byteidx == 1) ? 3 : (byteidx == 2) ? 0 : 2;
+    const int f = 4 * n + q;                       // code index inside the word, in use order
+    const int e = f % 8;                           // index among the lane's 8 codes of one 16x16 block
+    const uint64_t b = word_in_lane * (uint64_t)(4 / w) + (uint64_t)(f / 8);   // 16x16 block, packing order
+    const uint32_t k = (uint32_t)(b % 4);
+    const uint64_t ij = b / 4;
+    const uint32_t i = (uint32_t)(ij / (cols / 16)), j = (uint32_t)(ij % (cols / 16));
+    const uint32_t g = (uint32_t)lane / 4, t = (uint32_t)lane % 4;
+    FieldSource s;
+    s.row = 64 * i + 16 * k + 8 * (uint32_t)((e / 2) % 2) + g;
+    s.col = 16 * j + 8 * (uint32_t)(e / 4) + 2 * t + (uint32_t)(e % 2);
+    return s;
+}
+
+// The bw-bit code at column c of a row stored as an MSB-first bit stream.
+FPX_HD uint32_t read_code(const uint8_t* row, uint32_t c, int bw) {
+    const uint32_t bit = c * (uint32_t)bw;
+    const uint32_t byte = bit >> 3, off = bit & 7;
+    uint32_t two = (uint32_t)row[byte] << 8;
+    if (off + (uint32_t)bw > 8) two |= row[byte + 1];
+    return (two >> (16 - off - (uint32_t)bw)) & ((1u << bw) - 1u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Dequantisation of four codes at a time, as raw fp16 bit patterns before any scaling.
+//
+// A code becomes the fp16 pattern  sign | (exponent,mantissa bits) >> (5 - E)  (the reference's
+// FPx_FP16_Cast_4Way, utils_parallel_dequant.cuh:13-28), so for E=3,M=2 the high byte of the fp16
+// is [s 0 0 e2 e1 e0 m1 m0] and for E=2,M=2 it is [s 0 0 0 e1 e0 m1 m0]; the low byte is zero.
+// The value is then 2^-(16 - 2^(E-1)) times the FPx value.
+//
+// `hi4` holds in every byte the 4-bit segment of one code (already masked to the low nibble).
+// For e3m2, `s_src` has the sign at bit 7 of every byte and `e_src` has e2 at bit 4 of every byte
+// (other bits arbitrary).  For e2m2, `s_src` has the sign at bit 7 (e_src unused).
+// Returns the four high bytes; out_lo/out_hi expand them into two half2 patterns:
+//   out_lo = (byte1 -> low half, byte3 -> high half), out_hi = (byte0 -> low half, byte2 -> high half).
+FPX_HD uint32_t stitch_e3m2(uint32_t s_src, uint32_t e_src, uint32_t nib) {
+    return (s_src & 0x80808080u) | ((e_src & 0x10101010u) | nib);
+}
+FPX_HD uint32_t stitch_e2m2(uint32_t s_src, uint32_t nib) { return (s_src & 0x80808080u) | nib; }
+
+FPX_HD uint32_t expand_13(uint32_t y) {   // bytes 3,1 -> high bytes of the two halves
+#if defined(__CUDA_ARCH__)
+    return __byte_perm(y, 0u, 0x3414);
+#else
+    return y & 0xff00ff00u;
+#endif
+}
+FPX_HD uint32_t expand_02(uint32_t y) {   // bytes 2,0 -> high bytes of the two halves
+#if defined(__CUDA_ARCH__)
+    return __byte_perm(y, 0u, 0x2404);
+#else
+    return (y << 8) & 0xff00ff00u;
+#endif
+}
+
+// Unpack the 16 codes that one lane owns in two vertically adjacent 16x16 blocks (sub-blocks
+// 2h and 2h+1 of a 64-row block, same 16 columns) into eight half2 bit patterns
+//   out[4*kk + 0..3] = A-fragment registers a0..a3 of sub-block 2h+kk:
+//   a0 = (row g,   cols 2t,2t+1)   a1 = (row g+8, cols 2t,2t+1)
+//   a2 = (row g,   cols 2t+8,2t+9) a3 = (row g+8, cols 2t+8,2t+9)
+// w4a / w4b: the lane's 4-bit words of sub-blocks 2h and 2h+1.
+// w2: the lane's 2-bit word that covers both sub-blocks (e3m2 only).
+// w1: the lane's 1-bit word of the column block, which covers all four sub-blocks (e2m2 only);
+//     h selects its upper (h=0) or lower (h=1) half of the iterations.
+template <int E_BITS>
+FPX_HD void unpack16(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, int h, uint32_t out[8]) {
+    const uint32_t nib0 = (w4a >> 4) & 0x0f0f0f0fu, nib1 = w4a & 0x0f0f0f0fu;
+    const uint32_t nib2 = (w4b >> 4) & 0x0f0f0f0fu, nib3 = w4b & 0x0f0f0f0fu;
+    uint32_t y0, y1, y2, y3;
+    if (E_BITS == 3) {
+        // iteration n' (0..3) has the sign at bit 7-2n' and e2 at bit 6-2n' of every byte of w2
+        y0 = stitch_e3m2(w2, w2 >> 2, nib0);
+        y1 = stitch_e3m2(w2 << 2, w2, nib1);
+        y2 = stitch_e3m2(w2 << 4, w2 << 2, nib2);
+        y3 = stitch_e3m2(w2 << 6, w2 << 4, nib3);
+    } else {
+        // iteration i (0..7) of the column block has the sign at bit 7-i; this lane pair uses 4h..4h+3
+        const uint32_t s = w1 << (4 * h);
+        y0 = stitch_e2m2(s, nib0);
+        y1 = stitch_e2m2(s << 1, nib1);
+        y2 = stitch_e2m2(s << 2, nib2);
+        y3 = stitch_e2m2(s << 3, nib3);
+    }
+    out[0] = expand_13(y0); out[1] = expand_02(y0); out[2] = expand_13(y1); out[3] = expand_02(y1);
+    out[4] = expand_13(y2); out[5] = expand_02(y2); out[6] = expand_13(y3); out[7] = expand_02(y3);
+}
+
+// 2^(16 - 2^(E-1)) as an fp16 bit pattern: 2^12 for E=3, 2^14 for E=2
+// (the reference's BIAS, utils_parallel_dequant.cuh:32-33).
+FPX_HD constexpr uint16_t bias_half_bits(int e_bits) {
+    return (uint16_t)(((16 - (1 << (e_bits - 1))) + 15) << 10);
+}
+
+// Split-K: K is cut in 64-wide blocks; split z of `splits` gets base (+1 for the first `extra`)
+// blocks, like the reference kernel (fp6_llm/csrc/include/kernel_matmul.cuh:60-70).
+FPX_HD void split_range(uint32_t k_blocks, uint32_t splits, uint32_t z, uint32_t* begin, uint32_t* count) {
+    const uint32_t base = k_blocks / splits, extra = k_blocks % splits;
+    *count = base + (z < extra ? 1u : 0u);
+    *begin = z * base + (z < extra ? z : extra);
+}
+
+}  // namespace fpx

@@ -1,0 +1,236 @@
+"""Python operators with the reference's names, argument order and meaning (fp6_llm/__init__.py:1-23,
+fp6_llm/csrc/pybind.cpp:9-15), implemented on the C interface of libfp6_b200.so.
+
+torch is used for device memory and streams only.  All compute runs in the library's CUDA kernels;
+there is no CPU implementation behind these functions, so a machine without a CUDA device raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _native
+from .formats import bit_width, check_format
+
+
+# ----------------------------------------------------------------------------- reference heuristic
+def Num_Wave(M, N, SplitK, Num_GPU_SMs):
+    """Same formula as the reference (fp6_llm/__init__.py:6-8): waves of its 256-row, 2-CTA/SM kernel."""
+    return math.ceil(M / 512) * math.ceil(N / 64) * SplitK / Num_GPU_SMs
+
+
+def HeuristicFuntion_SplitK(M, N, Num_GPU_SMs):
+    """The reference's split-K choice, unchanged (fp6_llm/__init__.py:13-23): the first k in 1..99 whose
+    last wave is at least 80 % full, else 1.  M = weight rows, N = batch.  The name keeps the reference's
+    spelling.  For this library's own kernel on B200 use :func:`heuristic_split_k_b200`."""
+    split_k = 1
+    for i in range(1, 100):
+        waves = Num_Wave(M, N, i, Num_GPU_SMs)
+        if waves / math.ceil(waves) >= 0.8:
+            split_k = i
+            break
+    return split_k
+
+
+def heuristic_split_k_b200(M: int, N: int, K: int, num_sms: int = 148) -> int:
+    """Split-K for the sm_100a kernel: 128-row tiles, 1 or 2 CTAs per SM, K-aware (C: fp6b200_choose_split_k)."""
+    return int(_native.lib().fp6b200_choose_split_k(M, N, K, num_sms))
+
+
+# ----------------------------------------------------------------------------- helpers
+def _require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise RuntimeError("fp6_llm_b200 needs a CUDA device (sm_100a); there is no CPU implementation")
+
+
+def _stream_ptr(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr())
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Grow-only fp32 split-K workspace per device (the reference allocates one per call,
+    fp6_llm/csrc/fp6_linear.cu:185-187).  Calls that share it must be ordered on one stream."""
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() * 4 < nbytes:
+        ws = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def _in_channels(weights: torch.Tensor, e_bits: int, m_bits: int) -> int:
+    bw = bit_width(e_bits, m_bits)
+    if weights.dim() != 2 or (weights.shape[1] * 32) % bw:
+        raise ValueError(f"weight tensor of shape {tuple(weights.shape)} is not [OC, IC/32*{bw}]")
+    return weights.shape[1] * 32 // bw
+
+
+# ----------------------------------------------------------------------------- linear layer
+def linear_forward_eXmY_cuda(EXPONENT: int, MANTISSA: int, _in_feats: torch.Tensor, _weights: torch.Tensor,
+                             _scales: torch.Tensor, splitK: int = 1) -> torch.Tensor:
+    """Out[B, OC] = In[B, IC] @ dequant(W)[OC, IC]^T  (fp_eXmY_linear_forward_cuda,
+    fp6_llm/csrc/fp6_linear.cu:269-313).
+
+    _in_feats  fp16 [B, IC] cuda;  _weights  int32 [OC, IC/32*(1+E+M)] cuda, prepacked;
+    _scales    fp16 [OC] cuda;     splitK >= 1 as in the reference, 0 = let the library choose.
+    Runs on the current torch stream (the reference uses the legacy default stream)."""
+    _require_cuda()
+    check_format(EXPONENT, MANTISSA)
+    if _in_feats.dtype != torch.float16 or _scales.dtype != torch.float16 or _weights.dtype != torch.int32:
+        raise ValueError("expected fp16 activations, int32 packed weights and fp16 scales")
+    if not (_in_feats.is_cuda and _weights.is_cuda and _scales.is_cuda):
+        raise ValueError("all tensors must be CUDA tensors")
+    if not (_in_feats.device == _weights.device == _scales.device):
+        raise ValueError("all tensors must be on the same device")
+    if _in_feats.dim() != 2:
+        raise ValueError("activations must be [B, IC]")
+    if not (_in_feats.is_contiguous() and _weights.is_contiguous() and _scales.is_contiguous()):
+        raise ValueError("tensors must be contiguous")
+    B, IC = _in_feats.shape
+    OC = _weights.shape[0]
+    if _in_channels(_weights, EXPONENT, MANTISSA) != IC:
+        raise ValueError(f"K mismatch: activations have IC={IC}, weights encode IC={_in_channels(_weights, EXPONENT, MANTISSA)}")
+    if IC % 64 or OC % 256 or B < 1:
+        raise ValueError("need IC % 64 == 0, OC % 256 == 0 and B >= 1")
+    if _scales.numel() != OC:
+        raise ValueError("scales must have OC elements")
+    if splitK < 0:
+        raise ValueError("splitK must be >= 0")
+    dev = _in_feats.device
+    L = _native.lib()
+    with torch.cuda.device(dev):
+        nbytes = L.fp6b200_workspace_bytes(OC, B, IC, splitK)
+        ws = _workspace(dev, nbytes) if nbytes else None
+        out = torch.empty((B, OC), dtype=torch.float16, device=dev)
+        rc = L.fp6b200_linear(EXPONENT, MANTISSA, _stream_ptr(dev), _ptr(_weights), _ptr(_scales), _ptr(_in_feats),
+                              _ptr(out), OC, B, IC, _ptr(ws) if ws is not None else None, splitK)
+    _native.check(rc, "fp6b200_linear")
+    return out
+
+
+def linear_forward_cuda(*args) -> torch.Tensor:
+    """FP6 (e3m2) linear layer (fp6_linear_forward_cuda, fp6_llm/csrc/fp6_linear.cu:161-201).
+
+    Code order, as bound by the reference (fp6_llm/csrc/pybind.cpp:9): (activation, packed_weight, scale, splitK).
+    The order printed in the reference's README, (packed_weight, scale, activation, splitK), is accepted too and
+    told apart by the dtype of the first argument."""
+    if len(args) == 3:
+        args = (*args, 1)
+    if len(args) != 4:
+        raise TypeError("linear_forward_cuda(activation, packed_weight, scale, splitK)")
+    a, b, c, split_k = args
+    if isinstance(a, torch.Tensor) and a.dtype == torch.int32:   # README order
+        a, b, c = c, a, b
+    return linear_forward_eXmY_cuda(3, 2, a, b, c, int(split_k))
+
+
+# ----------------------------------------------------------------------------- prepacking
+def weight_prepacking_eXmY_cpu(EXPONENT: int, MANTISSA: int, fpx_tensor: torch.Tensor) -> torch.Tensor:
+    """Unpacked int32 [OC, IC/32*bw] -> prepacked tensor of the same shape, bit-identical to the reference's
+    weight_matrix_prepacking_fp_eXmY_cpu (fp6_llm/csrc/fp6_linear.cu:323-341).
+
+    A CPU tensor (the reference's case) is staged through the GPU and a CPU tensor comes back; a CUDA tensor
+    is packed in place on its device.  Either way the packing itself runs in the CUDA kernel."""
+    _require_cuda()
+    check_format(EXPONENT, MANTISSA)
+    if fpx_tensor.dtype != torch.int32 or fpx_tensor.dim() != 2:
+        raise ValueError("expected an int32 [OC, IC/32*bw] tensor")
+    IC = _in_channels(fpx_tensor, EXPONENT, MANTISSA)
+    OC = fpx_tensor.shape[0]
+    if OC % 256 or IC % 64:
+        raise ValueError("need OC % 256 == 0 and IC % 64 == 0")
+    src = fpx_tensor.contiguous()
+    out = torch.empty_like(src)
+    L = _native.lib()
+    if src.is_cuda:
+        with torch.cuda.device(src.device):
+            rc = L.fp6b200_prepack(EXPONENT, MANTISSA, _stream_ptr(src.device), _ptr(src), _ptr(out), OC, IC)
+    else:
+        rc = L.fp6b200_prepack_host(EXPONENT, MANTISSA, _ptr(out), _ptr(src), OC, IC)
+    _native.check(rc, "fp6b200_prepack")
+    return out
+
+
+def weight_prepacking_cpu(fp6_tensor: torch.Tensor) -> torch.Tensor:
+    """FP6 case of :func:`weight_prepacking_eXmY_cpu` (weight_matrix_prepacking_cpu, fp6_llm/csrc/fp6_linear.cu:211-223)."""
+    return weight_prepacking_eXmY_cpu(3, 2, fp6_tensor)
+
+
+# ----------------------------------------------------------------------------- dequantisation
+def weight_dequant_eXmY_cpu(EXPONENT: int, MANTISSA: int, fpx_tensor: torch.Tensor, fp16_scale: torch.Tensor) -> torch.Tensor:
+    """UNPACKED int32 [OC, IC/32*bw] + fp16 scale [OC] -> fp16 [OC, IC], bit-identical to the reference's
+    weight_matrix_dequant_fp_eXmY_cpu (fp6_llm/csrc/fp6_linear.cu:352-375).  CPU tensors are staged through
+    the GPU; CUDA tensors stay on their device."""
+    _require_cuda()
+    check_format(EXPONENT, MANTISSA)
+    if fpx_tensor.dtype != torch.int32 or fp16_scale.dtype != torch.float16:
+        raise ValueError("expected int32 weights and fp16 scales")
+    IC = _in_channels(fpx_tensor, EXPONENT, MANTISSA)
+    OC = fpx_tensor.shape[0]
+    if fp16_scale.numel() != OC:
+        raise ValueError("scales must have OC elements")
+    if OC % 64 or IC % 64:
+        raise ValueError("need OC % 64 == 0 and IC % 64 == 0")
+    if fpx_tensor.device != fp16_scale.device:
+        raise ValueError("weights and scales must be on the same device")
+    src, sc = fpx_tensor.contiguous(), fp16_scale.contiguous()
+    out = torch.empty((OC, IC), dtype=torch.float16, device=src.device)
+    L = _native.lib()
+    if src.is_cuda:
+        with torch.cuda.device(src.device):
+            rc = L.fp6b200_dequant(EXPONENT, MANTISSA, _stream_ptr(src.device), _ptr(src), _ptr(sc), _ptr(out), OC, IC)
+    else:
+        rc = L.fp6b200_dequant_host(EXPONENT, MANTISSA, _ptr(out), _ptr(src), OC, IC, _ptr(sc))
+    _native.check(rc, "fp6b200_dequant")
+    return out
+
+
+def weight_dequant_cpu(fp6_tensor: torch.Tensor, fp16_scale: torch.Tensor) -> torch.Tensor:
+    """FP6 case of :func:`weight_dequant_eXmY_cpu` (weight_matrix_dequant_cpu, fp6_llm/csrc/fp6_linear.cu:234-251)."""
+    return weight_dequant_eXmY_cpu(3, 2, fp6_tensor, fp16_scale)
+
+
+def dequant_packed_cuda(EXPONENT: int, MANTISSA: int, packed: torch.Tensor, fp16_scale: torch.Tensor) -> torch.Tensor:
+    """PREPACKED int32 weights (cuda) + scales -> fp16 [OC, IC]: the matrix the GEMM multiplies by.  Not in the
+    reference (its GPU dequantiser only exists fused in the GEMM); used for fp16-GEMM comparisons."""
+    _require_cuda()
+    check_format(EXPONENT, MANTISSA)
+    if not packed.is_cuda or packed.dtype != torch.int32 or fp16_scale.dtype != torch.float16:
+        raise ValueError("expected cuda int32 packed weights and fp16 scales")
+    IC = _in_channels(packed, EXPONENT, MANTISSA)
+    OC = packed.shape[0]
+    out = torch.empty((OC, IC), dtype=torch.float16, device=packed.device)
+    with torch.cuda.device(packed.device):
+        rc = _native.lib().fp6b200_dequant_packed(EXPONENT, MANTISSA, _stream_ptr(packed.device), _ptr(packed.contiguous()),
+                                                  _ptr(fp16_scale.contiguous()), _ptr(out), OC, IC)
+    _native.check(rc, "fp6b200_dequant_packed")
+    return out
+
+
+def linear_forward_host(EXPONENT: int, MANTISSA: int, act_host: torch.Tensor, packed_dev: torch.Tensor,
+                        scales_dev: torch.Tensor, out_host: torch.Tensor, splitK: int = 0) -> torch.Tensor:
+    """The layer with HOST activations/output (ideally pinned) and device-resident weights: host->device copy,
+    kernels, device->host copy, synchronise (C: fp6b200_linear_host_io)."""
+    _require_cuda()
+    B, IC = act_host.shape
+    OC = packed_dev.shape[0]
+    with torch.cuda.device(packed_dev.device):
+        rc = _native.lib().fp6b200_linear_host_io(EXPONENT, MANTISSA, _ptr(packed_dev), _ptr(scales_dev), _ptr(act_host),
+                                                  _ptr(out_host), OC, B, IC, splitK)
+    _native.check(rc, "fp6b200_linear_host_io")
+    return out_host
+
+
+def device_status() -> int:
+    """Synchronise and return (then clear) the time-out code a GEMM CTA may have recorded; 0 = healthy."""
+    code = ctypes.c_int(0)
+    _native.check(_native.lib().fp6b200_device_status(ctypes.byref(code)), "fp6b200_device_status")
+    return code.value

@@ -1,0 +1,111 @@
+/*
+ * C interface of libfp6_b200.so: the FPx (FP6 e3m2 / FP5 e2m2) x FP16 linear layer for NVIDIA B200.
+ *
+ * Every entry point takes plain pointers and sizes and returns a cudaError_t value as int
+ * (0 = success); nothing here allocates on behalf of the caller except the *_host helpers, which
+ * stage through a private, grow-only device buffer.  Each declaration names the function of the
+ * reference project (usyd-fsalab/fp6_llm, paths relative to its tree) that it stands in for.
+ *
+ * Matrix convention (same as the reference): M = output channels (rows of the weight matrix),
+ * K = input channels, N = tokens.  Out[N][M] (fp16, row-major) = Act[N][K] * dequant(W)[M][K]^T.
+ * Constraints (same as the reference, fp6_llm/csrc/fp6_linear.cu:56-58): M % 256 == 0,
+ * K % 64 == 0, N > 0, (e_bits, m_bits) in {(3,2), (2,2)}.
+ * Packed weights are the reference's layout, int32 [M][K/32*(1+e_bits+m_bits)] viewed as one flat
+ * buffer [1-bit region][2-bit region][4-bit region]
+ * (fp6_llm/csrc/utils/weight_prepacking.h:126-133).
+ */
+#ifndef FP6_LLM_B200_H_
+#define FP6_LLM_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Library interface version (bumped on any signature change). */
+int fp6b200_version(void);
+
+/* Text for a code returned by any function below. */
+const char* fp6b200_error_string(int code);
+
+/*
+ * The linear layer on device buffers, asynchronous on `stream` (a cudaStream_t).
+ * Stands in for fp_eXmY_linear_kernel (fp6_llm/csrc/fp6_linear.cuh:20-32; with e_bits=3, m_bits=2
+ * also for fp6_linear_kernel, :8-18).  `workspace` holds split_k*M*N floats and is only touched
+ * when split_k > 1.  split_k == 0 lets the library pick (fp6b200_choose_split_k with the SM count of
+ * the current device); size the workspace with fp6b200_workspace_bytes(M, N, K, 0) in that case.
+ * Unsupported shapes/formats return cudaErrorInvalidValue instead of asserting or exiting.
+ */
+int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,
+                   const void* act, void* out, size_t M, size_t N, size_t K, float* workspace, int split_k);
+
+/*
+ * Same layer with HOST activations and output: copies act to the device, runs the layer, copies the
+ * result back and synchronises.  Weights and scales stay resident on the device (they are parameters).
+ * Stands in for the torch-level call fp_eXmY_linear_forward_cuda (fp6_llm/csrc/fp6_linear.cu:269-313)
+ * when the caller's tensors live in host memory.
+ */
+int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev, const void* scales_dev,
+                           const void* act_host, void* out_host, size_t M, size_t N, size_t K, int split_k);
+
+/* Bytes of split-K workspace fp6b200_linear needs (split_k == 0: for the library's own choice). */
+size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k);
+
+/*
+ * Split-K choice for this kernel on a GPU with `num_sms` SMs (148 on B200); accounts for the 128-row
+ * tiles, the CTAs resident per SM and the K blocks available.  The reference's own heuristic
+ * (HeuristicFuntion_SplitK, fp6_llm/__init__.py:13-23) is kept separately, unchanged, in Python.
+ */
+int fp6b200_choose_split_k(size_t M, size_t N, size_t K, int num_sms);
+
+/*
+ * Weight prepacking on device buffers (in != out), asynchronous on `stream`.
+ * GPU counterpart of weight_matrix_prepacking_fp_eXmY (fp6_llm/csrc/utils/weight_prepacking.h:204-211);
+ * the output is bit-identical.  Needs M % 64 == 0 and K % 64 == 0 (:121-122).
+ */
+int fp6b200_prepack(int e_bits, int m_bits, void* stream, const void* unpacked_dev, void* packed_dev, size_t M,
+                    size_t K);
+
+/*
+ * Same with host buffers (in == out allowed), synchronous.  Drop-in for
+ * weight_matrix_prepacking_fp_eXmY(E, M, packed, unpacked, M, K) and weight_matrix_prepacking
+ * (fp6_llm/csrc/fp6_linear.cuh:37-38).
+ */
+int fp6b200_prepack_host(int e_bits, int m_bits, int* packed_host, const int* unpacked_host, size_t M, size_t K);
+
+/*
+ * UNPACKED weights + per-row fp16 scales -> fp16 [M][K], device buffers.
+ * GPU counterpart of dequant_matrix_fp_eXmY_to_fp16 (fp6_llm/csrc/utils/weight_dequant.h:54-61); bit-identical.
+ */
+int fp6b200_dequant(int e_bits, int m_bits, void* stream, const void* unpacked_dev, const void* scales_dev,
+                    void* out_dev, size_t M, size_t K);
+
+/* Same with host buffers, synchronous.  Drop-in for dequant_matrix_fp_eXmY_to_fp16 and
+ * DeQuantMatrix_FP6_To_FP16 (fp6_llm/csrc/fp6_linear.cuh:42-43). */
+int fp6b200_dequant_host(int e_bits, int m_bits, void* out_host, const void* unpacked_host, size_t M, size_t K,
+                         const void* scales_host);
+
+/*
+ * PREPACKED weights + scales -> fp16 [M][K], device buffers: what the GEMM multiplies by, element for
+ * element.  The reference has no such function; its GPU dequantiser is fused in the GEMM
+ * (fp6_llm/csrc/include/utils_parallel_dequant.cuh:44-99), which is the code this mirrors.
+ */
+int fp6b200_dequant_packed(int e_bits, int m_bits, void* stream, const void* packed_dev, const void* scales_dev,
+                           void* out_dev, size_t M, size_t K);
+
+/* out[i] = rn_half(sum_s partials[s*elems + i]), ascending s, fp32.  Stands in for SplitK_Reduction
+ * (fp6_llm/csrc/include/kernel_reduction.cuh:28-47).  elems % 4 == 0. */
+int fp6b200_splitk_reduce(void* stream, void* out_dev, const float* partials_dev, size_t elems, int split_k);
+
+/*
+ * Synchronises the current device, returns in *code the first time-out code a GEMM CTA recorded
+ * since the last call (0 = none) and clears it.  A non-zero code means a bounded wait inside the
+ * kernel gave up and the output of that launch is invalid.
+ */
+int fp6b200_device_status(int* code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP6_LLM_B200_H_ */

@@ -1,0 +1,27 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+@pytest.fixture(scope="session")
+def oracle_mod():
+    import oracle
+    oracle.lib()   # builds the C restatement on first use
+    return oracle
+
+
+@pytest.fixture(scope="session")
+def native_lib():
+    """The CUDA library, built if needed (nvcc cross-compiles without a GPU)."""
+    import fp6_llm_b200
+    fp6_llm_b200.build()
+    return fp6_llm_b200.lib()

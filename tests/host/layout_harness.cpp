@@ -1,0 +1,84 @@
+// Host build of the integer-only layout/unpack code the CUDA kernels use (fp6_llm_b200/csrc/fpx_layout.h),
+// so the index arithmetic can be checked against the CPU oracle without a GPU.  Test code only.
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "../../fp6_llm_b200/csrc/fpx_layout.h"
+
+using namespace fpx;
+
+extern "C" {
+
+// The prepack kernel's gather, word by word.
+int harness_prepack(int e_bits, int m_bits, uint8_t* out, const uint8_t* in, uint32_t rows, uint32_t cols) {
+    const int bw = 1 + e_bits + m_bits;
+    const size_t row_bytes = (size_t)cols * bw / 8;
+    std::vector<uint8_t> padded((size_t)rows * row_bytes + 1, 0);
+    std::memcpy(padded.data(), in, (size_t)rows * row_bytes);
+    for (int w = 1; w <= 4; w <<= 1) {
+        if (!has_seg(bw, w)) continue;
+        uint32_t* region = reinterpret_cast<uint32_t*>(out + region_offset(bw, w, rows, cols));
+        const uint64_t words_per_lane = (uint64_t)rows * cols * w / 8 / 4 / 32;
+        for (uint64_t wl = 0; wl < words_per_lane; wl++)
+            for (int lane = 0; lane < 32; lane++) {
+                uint32_t word = 0;
+                for (int p = 0; p < 32 / w; p++) {
+                    FieldSource s = field_source(w, wl, lane, p, cols);
+                    uint32_t code = read_code(padded.data() + (size_t)s.row * row_bytes, s.col, bw);
+                    word |= ((code >> seg_shift(bw, w)) & ((1u << w) - 1u)) << (32 - (p + 1) * w);
+                }
+                region[wl * 32 + lane] = word;
+            }
+    }
+    return 0;
+}
+
+// The GEMM's unpack path: for every 128-row tile, 64-wide K block, tensor-memory quadrant q and lane, read
+// the words the kernel reads (stage layout = [segment][row block][word]), run unpack16 and scatter the
+// registers the way tcgen05.st.16x128b.x8 places them (thread 4g+t, register 2c+hr -> lane g+8hr, 32-bit
+// column t+4c).  out_bits[row*cols+col] receives the unscaled fp16 pattern.
+int harness_unpack(int e_bits, int m_bits, uint16_t* out_bits, const uint8_t* packed, uint32_t rows, uint32_t cols) {
+    const int bw = 1 + e_bits + m_bits;
+    if (rows % 128 || cols % 64) return -1;
+    const uint32_t kblocks = cols / 64;
+    for (uint32_t m_tile = 0; m_tile < rows / 128; m_tile++)
+        for (uint32_t kb = 0; kb < kblocks; kb++)
+            for (int q = 0; q < 4; q++)
+                for (int lane = 0; lane < 32; lane++) {
+                    const int h = q & 1, rb = q >> 1, g = lane >> 2, t = lane & 3;
+                    const uint64_t tile = (uint64_t)(m_tile * 2 + rb) * kblocks + kb;
+                    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(packed + region_offset(bw, 1, rows, cols) + tile * tile_bytes(1));
+                    const uint32_t* r2 = reinterpret_cast<const uint32_t*>(packed + region_offset(bw, 2, rows, cols) + tile * tile_bytes(2));
+                    const uint32_t* r4 = reinterpret_cast<const uint32_t*>(packed + region_offset(bw, 4, rows, cols) + tile * tile_bytes(4));
+                    uint32_t v[2][16];
+                    for (int j = 0; j < 4; j++) {
+                        uint32_t w4a = r4[(j * 4 + 2 * h + 0) * 32 + lane], w4b = r4[(j * 4 + 2 * h + 1) * 32 + lane];
+                        uint32_t w2 = has_seg(bw, 2) ? r2[(j * 2 + h) * 32 + lane] : 0u;
+                        uint32_t w1 = has_seg(bw, 1) ? r1[j * 32 + lane] : 0u;
+                        uint32_t pat[8];
+                        if (e_bits == 3) unpack16<3>(w4a, w4b, w2, w1, h, pat); else unpack16<2>(w4a, w4b, w2, w1, h, pat);
+                        for (int kk = 0; kk < 2; kk++)
+                            for (int i = 0; i < 4; i++) v[kk][4 * j + i] = pat[4 * kk + i];
+                    }
+                    for (int kk = 0; kk < 2; kk++)
+                        for (int reg = 0; reg < 16; reg++) {
+                            const int c = reg / 2, hr = reg % 2;
+                            const uint32_t tm_lane = 32 * q + 16 * kk + g + 8 * hr;     // tensor-memory lane = tile row
+                            const uint32_t col32 = t + 4 * c;                            // 32-bit column = K pair
+                            const uint32_t row = m_tile * 128 + tm_lane;
+                            const uint32_t col = kb * 64 + 2 * col32;
+                            out_bits[(size_t)row * cols + col] = (uint16_t)(v[kk][reg] & 0xffffu);
+                            out_bits[(size_t)row * cols + col + 1] = (uint16_t)(v[kk][reg] >> 16);
+                        }
+                }
+    return 0;
+}
+
+void harness_split_range(uint32_t k_blocks, uint32_t splits, uint32_t z, uint32_t* begin, uint32_t* count) {
+    split_range(k_blocks, splits, z, begin, count);
+}
+
+uint16_t harness_bias_bits(int e_bits) { return bias_half_bits(e_bits); }
+
+}  // extern "C"

@@ -1,0 +1,61 @@
+"""The integer layout/unpack code shared with the CUDA kernels (fp6_llm_b200/csrc/fpx_layout.h), compiled for the
+host and compared with the oracle: the prepack gather, the registers every lane of the GEMM produces and where the
+tensor-memory store puts them, and the split-K ranges."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from helpers import FORMATS, random_unpacked
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def harness(tmp_path_factory):
+    so = str(tmp_path_factory.mktemp("harness") / "liblayout_harness.so")
+    subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", so,
+                    os.path.join(HERE, "host", "layout_harness.cpp")], check=True)
+    return ctypes.CDLL(so)
+
+
+@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("rows,cols", [(128, 64), (256, 192), (384, 320)])
+def test_prepack_gather_matches_oracle(harness, oracle_mod, e, m, rows, cols):
+    rng = np.random.default_rng(rows + cols + e)
+    w = random_unpacked(rng, rows, cols, e, m)
+    out = np.zeros_like(w)
+    assert harness.harness_prepack(e, m, ctypes.c_void_p(out.ctypes.data), ctypes.c_void_p(w.ctypes.data), rows, cols) == 0
+    assert np.array_equal(out, oracle_mod.prepack(w, e, m))
+
+
+@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("rows,cols", [(128, 64), (256, 256)])
+def test_gemm_unpack_registers(harness, oracle_mod, e, m, rows, cols):
+    rng = np.random.default_rng(rows * 3 + cols + e)
+    w = random_unpacked(rng, rows, cols, e, m)
+    packed = oracle_mod.prepack(w, e, m)
+    bits = np.zeros((rows, cols), np.uint16)
+    assert harness.harness_unpack(e, m, ctypes.c_void_p(bits.ctypes.data), ctypes.c_void_p(packed.ctypes.data), rows, cols) == 0
+    expect = oracle_mod.dequant(w, np.ones(rows, np.float16), e, m).astype(np.float32)
+    bias = np.array([harness.harness_bias_bits(e)], np.uint16).view(np.float16).astype(np.float32)[0]
+    assert bias == 2.0 ** (16 - 2 ** (e - 1))
+    got = bits.view(np.float16).astype(np.float32) * bias
+    assert np.array_equal(got, expect) and np.array_equal(np.signbit(got), np.signbit(expect))
+
+
+def test_split_ranges_cover_k(harness):
+    harness.harness_split_range.argtypes = [ctypes.c_uint32] * 3 + [ctypes.POINTER(ctypes.c_uint32)] * 2
+    for kb in (1, 2, 7, 64, 172, 448):
+        for splits in (1, 2, 3, 7, kb, kb + 3):
+            nxt = 0
+            for z in range(splits):
+                b, c = ctypes.c_uint32(), ctypes.c_uint32()
+                harness.harness_split_range(kb, splits, z, ctypes.byref(b), ctypes.byref(c))
+                # reference: avg (+1 for the first `extra` splits), fp6_llm/csrc/include/kernel_matmul.cuh:60-70
+                assert c.value == kb // splits + (1 if z < kb % splits else 0)
+                assert b.value == nxt
+                nxt += c.value
+            assert nxt == kb
