@@ -234,10 +234,8 @@ def run_ours(args):
                            for r in range(n_rep)]
     acts = {(mdl["name"], bs): torch.randn(bs, mdl["ic"], device=dev, dtype=torch.float16) for mdl in models for bs in batches}
     cases = [(mdl, bs) for bs in batches for mdl in models]
-    split = {}
-    for mdl, bs in cases:
-        local_oc = mdl["plan"][rank][1] - mdl["plan"][rank][0]
-        split[(mdl["name"], bs)] = args.split_k if args.split_k > 0 else f.heuristic_split_k_b200(local_oc, bs, mdl["ic"], sms)
+    # split_k = 0: the library decomposes the work itself (tile waves + stream-K remainder + fix-up kernel)
+    split = {(mdl["name"], bs): max(args.split_k, 0) for mdl, bs in cases}
     nb = len(batches)
 
     def run_step(step_index):
@@ -298,7 +296,7 @@ def run_ours(args):
     wbytes_step = sum(mdl["oc"] * mdl["ic"] * bw / 8 for mdl, bs in cases)
     abytes_step = sum(alg_bytes(mdl["oc"], mdl["ic"], bs, bw) for mdl, bs in cases)
     sec_step = ms_total / 1e3 / args.steps
-    launches_step = sum(1 + (1 if split[(mdl["name"], bs)] > 1 else 0) for mdl, bs in cases)
+    launches_step = sum(1 + (1 if split[(mdl["name"], bs)] != 1 else 0) for mdl, bs in cases)   # GEMM + reduce/fix-up
     hbm_peak, tc_peak, peak_kind = peaks()
 
     # ---- per-case device times (separate pass, each case alone in a graph of `replicas` launches)
@@ -376,7 +374,7 @@ def run_ours(args):
             "ms_per_step": sec_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": args.workload, "format": f"e{e}m{m}", "layers": [list(l) for l in layers], "batch_sizes": batches,
-                       "split_k": "library heuristic" if args.split_k <= 0 else args.split_k,
+                       "split_k": "0 (library: tile waves + stream-K remainder)" if args.split_k <= 0 else args.split_k,
                        "parallelism": "single GPU" if world == 1 else f"OC-sharded x{world} + all-gather of [BS, OC]",
                        "l2": f"inputs larger than L2: {replicas} replicas of the layer set ({shard_bytes * replicas / 2**20:.0f} MiB) rotated so a buffer is re-read only after >= 512 MiB of other weights",
                        "launch": "whole step replayed as a CUDA graph"},
@@ -399,7 +397,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
-    ap.add_argument("--split-k", type=int, default=0, help="0 = library heuristic")
+    ap.add_argument("--split-k", type=int, default=0, help="0 = let the library decompose the work")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

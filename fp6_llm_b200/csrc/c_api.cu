@@ -33,18 +33,6 @@ int* status_ptr() {
     return ptrs[dev];
 }
 
-int sm_count() {
-    static int counts[kMaxDevices] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
-    if (!counts[dev]) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        counts[dev] = n;
-    }
-    return counts[dev];
-}
-
 // Grow-only device staging buffer for the *_host entry points (one per device, calls are serialised).
 struct Staging {
     std::mutex mu;
@@ -81,26 +69,22 @@ cudaError_t staging_get(size_t bytes, void** out, cudaStream_t* stream) {
 }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Split count for callers that want the reference's explicit split-K scheme on this kernel: one CTA per SM,
+// 128-row tiles, items = tiles * split dealt round-robin.  Picks the split that minimises
+// ceil(items / SMs) * (K blocks per item + fixed cost per item), preferring small splits on ties.
 int choose_split_k(size_t M, size_t N, size_t K, int num_sms) {
     if (M == 0 || N == 0 || K < 64 || num_sms <= 0) return 1;
     const int n_tile = fpx::gemm_n_tile(N);
-    const double slots = (double)num_sms * fpx::gemm_ctas_per_sm(n_tile);
     const double tiles = (double)(M / 128) * (double)((N + n_tile - 1) / n_tile);
     const size_t kblocks = K / 64;
-    // Cost in units of "one 64-wide K block of one CTA": every CTA pays a fixed start-up/epilogue
-    // cost, a split adds a second kernel plus the fp32 partial round trip.
-    const double cta_overhead = 10.0;
-    const double reduce_launch = 12.0;
+    const double item_overhead = 6.0;    // pipeline fill + epilogue, in K-block units
     int best = 1;
     double best_cost = 1e300;
     const size_t max_split = kblocks < 32 ? kblocks : 32;
     for (size_t k = 1; k <= max_split; k++) {
-        const double waves = ceil(tiles * (double)k / slots);
-        const double per_cta = ceil((double)kblocks / (double)k) + cta_overhead;
-        // partial traffic: k*M*N*4 bytes written and read, versus 128*64*0.75 bytes per K block unit
-        const double partial = k > 1 ? reduce_launch + 2.0 * (double)k * (double)M * (double)N * 4.0 / (6144.0 * slots) : 0.0;
-        const double cost = waves * per_cta + partial;
-        if (cost < best_cost * 0.97) {   // prefer the smaller split unless the gain is clear
+        const double rounds = ceil(tiles * (double)k / (double)num_sms);
+        const double cost = rounds * (ceil((double)kblocks / (double)k) + item_overhead) + (k > 1 ? 8.0 : 0.0);
+        if (cost < best_cost * 0.97) {
             best_cost = cost;
             best = (int)k;
         }
@@ -119,13 +103,13 @@ const char* fp6b200_error_string(int code) { return cudaGetErrorString(static_ca
 int fp6b200_choose_split_k(size_t M, size_t N, size_t K, int num_sms) { return choose_split_k(M, N, K, num_sms); }
 
 size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k) {
-    if (split_k == 0) split_k = choose_split_k(M, N, K, sm_count());
+    (void)K;
+    if (split_k == 0) return fpx::gemm_auto_workspace_bytes(N);
     return split_k > 1 ? (size_t)split_k * M * N * sizeof(float) : 0;
 }
 
 int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,
                    const void* act, void* out, size_t M, size_t N, size_t K, float* workspace, int split_k) {
-    if (split_k == 0) split_k = choose_split_k(M, N, K, sm_count());
     int* status = status_ptr();
     if (!status) return cudaErrorInitializationError;
     return fpx::launch_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_packed,
@@ -135,11 +119,9 @@ int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_pack
 
 int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev, const void* scales_dev,
                            const void* act_host, void* out_host, size_t M, size_t N, size_t K, int split_k) {
-    if (!act_host || !out_host) return cudaErrorInvalidValue;
-    if (split_k == 0) split_k = choose_split_k(M, N, K, sm_count());
-    if (split_k < 1) return cudaErrorInvalidValue;
+    if (!act_host || !out_host || split_k < 0) return cudaErrorInvalidValue;
     const size_t act_bytes = align_up(N * K * sizeof(__half), 256), out_bytes = align_up(N * M * sizeof(__half), 256);
-    const size_t ws_bytes = split_k > 1 ? (size_t)split_k * M * N * sizeof(float) : 0;
+    const size_t ws_bytes = fp6b200_workspace_bytes(M, N, K, split_k);
     std::lock_guard<std::mutex> lock(staging().mu);
     void* base = nullptr;
     cudaStream_t stream = nullptr;

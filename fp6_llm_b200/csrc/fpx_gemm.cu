@@ -1,23 +1,25 @@
 // FPx (e3m2 / e2m2) x fp16 linear layer for sm_100a:  Out[N, M] = Act[N, K] * dequant(W)[M, K]^T.
 //
 // Replaces the reference's QUANT_GEMM_Kernel + launcher
-// (fp6_llm/csrc/include/kernel_matmul.cuh:29-191, fp6_llm/csrc/fp6_linear.cu:11-102) with a design
-// built around Blackwell's tensor memory:
+// (fp6_llm/csrc/include/kernel_matmul.cuh:29-191, fp6_llm/csrc/fp6_linear.cu:11-102) with a persistent,
+// warp-specialised kernel built around Blackwell's tensor memory.  One CTA per SM walks a list of
+// segments (output tile 128 x N_TILE, range of 64-wide K blocks; see WorkPlan in fpx_layout.h):
 //
-//   warp 0      streams the packed weight segments of one (128 rows x 64 K) stage with 1-D bulk
-//               copies into an 8-deep shared-memory ring (the packed layout keeps all of K
-//               contiguous per 64-row block and segment, so no tensor map is needed);
-//   warp 1      streams the activation tile [N_TILE x 64] with a 2-D TMA tensor copy (128-byte
-//               swizzle, rows past N zero-filled);
-//   warps 3-10  unpack the segments with shift/LOP3/PRMT sequences, apply 2^bias * scale[row] in
-//               fp16 and write the fp16 weights STRAIGHT INTO TENSOR MEMORY with
-//               tcgen05.st.16x128b: the reference's packed format hands every lane exactly the
-//               registers of an m16k16 A fragment, which is the register pattern of that store,
-//               so the dequantised weights never touch shared memory;
-//   warp 2      issues tcgen05.mma.kind::f16 with A from tensor memory and B from shared memory,
-//               accumulating fp32 in tensor memory;
-//   warps 3-10  finally read the accumulator with tcgen05.ld and store fp16 (or fp32 split-K
-//               partials) to global memory.
+//   warps 4-5   fill a deep shared-memory ring, one stage = 128 rows x 128 K (64 K for the widest tile):
+//               first the activation tile [N_TILE x 64] per K block with a 2-D TMA tensor copy (128-byte
+//               swizzle, rows past N zero-filled), then the packed weight segments with 1-D bulk copies
+//               (the packed layout keeps all of K contiguous per 64-row block and segment, so no tensor
+//               map is needed and one copy per segment and row block covers the whole stage);
+//   warps 6-21  unpack the segments with shift/LOP3/PRMT sequences, apply 2^bias * scale[row] in fp16
+//               and write the fp16 weights STRAIGHT INTO TENSOR MEMORY with tcgen05.st.16x128b: the
+//               reference's packed format hands every lane exactly the registers of an m16k16 A
+//               fragment, which is the register pattern of that store, so the dequantised weights
+//               never touch shared memory;
+//   warps 0-3   issue tcgen05.mma.kind::f16 with A from tensor memory and B from shared memory, accumulating
+//               fp32 in tensor memory; narrow tiles are issued by up to four warps, each into its own
+//               accumulator, because one thread cannot issue MMAs fast enough for them.  At the end of a
+//               segment the same four warps (one per tensor-memory lane quadrant) read the accumulators
+//               with tcgen05.ld, add them and store fp16 output or fp32 partials.
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records a code in a status word, drains its
 // own copies, frees its tensor memory and returns.
@@ -35,44 +37,94 @@ namespace fpx {
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kRawStages = 8;
-constexpr int kAStages = 4;
-constexpr int kAColsPerStage = 32;                       // 64 fp16 along K per tensor-memory lane
-constexpr int kAccColBase = kAStages * kAColsPerStage;   // accumulator columns follow the A ring
-constexpr int kFirstDequantWarp = 3;
-constexpr int kDequantWarps = 8;
+constexpr int kAColsPerKBlock = 32;      // 64 fp16 along K per tensor-memory lane
+constexpr int kMaxIssuers = 4;           // warps 0..3: MMA issuers (lane 0 of each) and, one per lane quadrant, the epilogue
+constexpr int kProducerWarp = 4;         // warps 4,5: one thread each; a thread can start a bulk copy only every ~100 cycles
+constexpr int kProducerWarps = 2;
+constexpr int kFirstDequantWarp = kProducerWarp + kProducerWarps;
+constexpr int kDequantGroups = 4;        // a group = 4 consecutive warps, one per tensor-memory lane quadrant
+constexpr int kDequantWarps = 4 * kDequantGroups;
+constexpr int kEpilogueWarps = 4;        // = warps 0..3
 constexpr int kWarps = kFirstDequantWarp + kDequantWarps;
 constexpr int kThreads = kWarps * 32;
+constexpr uint32_t kTmemCols = 512;      // the whole tensor memory: one CTA per SM
 
 // status codes written by a wait that gave up
 enum : int {
-    kErrRawEmpty = 1, kErrRawFull = 2, kErrBEmpty = 3, kErrBFull = 4, kErrAEmpty = 5, kErrAFull = 6, kErrAccFull = 7
+    kErrStageEmpty = 1, kErrStageFull = 2, kErrAEmpty = 3, kErrAFull = 6, kErrAccFull = 7, kErrSmemAlign = 8,
+    kErrAccEmpty = 9
 };
 
+// Packed bytes of one (64 rows x 64 K) block per segment width.
 template <int BW>
-struct RawStage {
+struct RawBlock {
     static constexpr uint32_t seg1 = (BW & 1) ? tile_bytes(1) : 0u;
     static constexpr uint32_t seg2 = (BW & 2) ? tile_bytes(2) : 0u;
     static constexpr uint32_t seg4 = (BW & 4) ? tile_bytes(4) : 0u;
-    // stage layout: [1-bit: row block 0, 1][2-bit: row block 0, 1][4-bit: row block 0, 1]
-    static constexpr uint32_t off1 = 0u;
-    static constexpr uint32_t off2 = 2u * seg1;
-    static constexpr uint32_t off4 = 2u * seg1 + 2u * seg2;
-    static constexpr uint32_t bytes = 2u * (seg1 + seg2 + seg4);
+    static constexpr uint32_t bytes128 = 2u * (seg1 + seg2 + seg4);   // 128 rows x 64 K
 };
 
-template <int N_TILE>
-struct BStage {
-    static constexpr uint32_t bytes = (uint32_t)N_TILE * 128u;
-    static constexpr int stages = N_TILE <= 32 ? 8 : (N_TILE <= 64 ? 6 : 4);
-};
-
+// A pipeline stage covers KS K blocks (64 wide each) of one 128-row tile:
+//   shared memory  [activations: KS x (N_TILE x 128 B, 128-byte swizzled)]
+//                  [weights, per segment width: row block 0: KS blocks, row block 1: KS blocks]
+//   tensor memory  KS x 32 columns of fp16 weights per stage of the A ring
 template <int BW, int N_TILE>
-struct Budget {
-    static constexpr uint32_t tmem_cols = (kAccColBase + N_TILE) <= 256 ? 256u : 512u;
-    static constexpr uint32_t smem_bytes =
-        1024u /* alignment slack */ + BStage<N_TILE>::stages * BStage<N_TILE>::bytes + kRawStages * RawStage<BW>::bytes +
-        (2 * kRawStages + 2 * BStage<N_TILE>::stages + 2 * kAStages + 1) * 8u + 16u;
+struct Config {
+    using Raw = RawBlock<BW>;
+    static constexpr int ks = N_TILE <= 128 ? 2 : 1;
+    static constexpr int stages = N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 7 : 5));
+    static constexpr int a_stages = N_TILE <= 64 ? 6 : (N_TILE <= 128 ? 4 : 5);
+    // when the A ring is as deep as the shared-memory ring one commit frees a whole stage
+    static constexpr bool unified = a_stages == stages;
+    // One thread can issue an MMA only every ~60-90 cycles, far more than a narrow MMA needs on the tensor
+    // pipe, so narrow tiles are issued by several warps, each into its own accumulator (summed in the epilogue).
+    static constexpr int issuers = N_TILE <= 32 ? 4 : (N_TILE <= 128 ? 2 : 1);
+    static constexpr int acc_bufs = 1;   // the issuing warps also run the epilogue, so one set of accumulators suffices
+    static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
+    static constexpr uint32_t w_off = ks * b_block;
+    static constexpr uint32_t off1 = w_off;
+    static constexpr uint32_t off2 = off1 + 2u * ks * Raw::seg1;
+    static constexpr uint32_t off4 = off2 + 2u * ks * Raw::seg2;
+    static constexpr uint32_t stage_bytes = ks * (b_block + Raw::bytes128);
+    static constexpr uint32_t a_cols = ks * kAColsPerKBlock;
+    static constexpr uint32_t acc_col0 = a_stages * a_cols;
+    static constexpr uint32_t acc_stride = N_TILE < 32 ? 32u : (uint32_t)N_TILE;
+    static constexpr int readers = 4 * ks;   // unpack warps per stage
+    static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
+    static_assert(acc_col0 + acc_bufs * issuers * acc_stride <= kTmemCols, "tensor memory budget");
+    static constexpr int num_barriers = 3 * stages + 2 * a_stages + 2 * acc_bufs;
+    static constexpr uint32_t smem_bytes = stages * stage_bytes + num_barriers * 8u + 16u;
+    static_assert(2u * smem_bytes > 228u * 1024u, "two CTAs must never share an SM: each takes all of tensor memory");
+    static_assert(smem_bytes <= 227u * 1024u, "shared memory budget");
+};
+
+// Optional per-role cycle counters (build with -DFPX_PROFILE): every role thread accumulates the cycles it
+// spends in each of its waits and in total, and leaves them in g_prof[cta][warp][counter].
+#ifdef FPX_PROFILE
+__device__ unsigned long long g_prof[160][kWarps][8];
+#define PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64();
+#define PROF_WAIT(slot, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); prof_acc[slot] += (unsigned long long)(clock64() - t_); return r_; }()
+#define PROF_BEGIN(var) const long long var = clock64();
+#define PROF_END(slot, var) prof_acc[slot] += (unsigned long long)(clock64() - var);
+#define PROF_COUNT(slot) prof_acc[slot]++;
+#define PROF_FLUSH() do { prof_acc[7] = (unsigned long long)(clock64() - prof_t0); if (lane == 0 && blockIdx.x < 160) for (int i_ = 0; i_ < 8; i_++) g_prof[blockIdx.x][warp][i_] = prof_acc[i_]; } while (0)
+#else
+#define PROF_DECL
+#define PROF_WAIT(slot, expr) (expr)
+#define PROF_BEGIN(var)
+#define PROF_END(slot, var)
+#define PROF_COUNT(slot)
+#define PROF_FLUSH() do { } while (0)
+#endif
+
+struct Params {
+    const uint8_t* weight;
+    const __half* scales;
+    __half* out;
+    float* workspace;
+    uint32_t M, N, K;
+    WorkPlan plan;
+    int* status;
 };
 
 __device__ __forceinline__ uint32_t scale_pair(uint32_t pat, __half2 c) {
@@ -81,250 +133,393 @@ __device__ __forceinline__ uint32_t scale_pair(uint32_t pat, __half2 c) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int BW, int N_TILE, bool PARTIAL>
-__global__ void __launch_bounds__(kThreads, (N_TILE <= 64) ? 2 : 1)
-fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __restrict__ weight,
-                const __half* __restrict__ scales, void* __restrict__ out, uint32_t M, uint32_t N, uint32_t K,
-                uint32_t split_k, int* __restrict__ status) {
+template <int BW, int N_TILE>
+__global__ void __launch_bounds__(kThreads, 1)
+fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
     constexpr int E_BITS = BW - 3;   // both supported formats have a 2-bit mantissa
-    using Raw = RawStage<BW>;
-    using BS = BStage<N_TILE>;
-    constexpr int SB = BS::stages;
-    constexpr int R = kRawStages;
-    constexpr int SA = kAStages;
+    using Cfg = Config<BW, N_TILE>;
+    using Raw = typename Cfg::Raw;
+    constexpr int KS = Cfg::ks;
+    constexpr int R = Cfg::stages;
+    constexpr int SA = Cfg::a_stages;
+    constexpr int NACC = Cfg::acc_bufs;
+    constexpr int NI = Cfg::issuers;
+    constexpr bool kUnified = Cfg::unified;
 
-    extern __shared__ uint8_t smem_dyn[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-    uint8_t* b_ring = smem;
-    uint8_t* raw_ring = b_ring + SB * BS::bytes;
-    uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + R * Raw::bytes);
-    uint64_t* raw_empty = raw_full + R;
-    uint64_t* b_full = raw_empty + R;
-    uint64_t* b_empty = b_full + SB;
-    uint64_t* a_full = b_empty + SB;
-    uint64_t* a_empty = a_full + SA;
-    uint64_t* acc_full = a_empty + SA;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
+    // 128-byte-swizzled tiles need a 1024-byte aligned base; the dynamic window starts at offset 0 of the
+    // CTA's shared memory (no static shared memory in this kernel), which is checked below.
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    // everything in shared memory is addressed by 32-bit shared-space addresses
+    const uint32_t ring = ptx::smem_u32(smem_dyn);
+    const uint32_t full = ring + R * Cfg::stage_bytes;   // barrier arrays, 8 bytes per barrier
+    const uint32_t w_empty = full + 8 * R;               // the unpack warps have read the weights of the stage
+    const uint32_t b_empty = w_empty + 8 * R;            // the MMAs that read the activations of the stage are done
+    const uint32_t a_full = b_empty + 8 * R;
+    const uint32_t a_empty = a_full + 8 * SA;
+    const uint32_t acc_full = a_empty + 8 * SA;
+    const uint32_t acc_empty = acc_full + 8 * NACC;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_dyn + R * Cfg::stage_bytes + 8 * Cfg::num_barriers);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t m_tile = blockIdx.x, n_tile = blockIdx.y, z = blockIdx.z;
-    uint32_t kb_begin, nkb;
-    split_range(K / kKBlock, split_k, z, &kb_begin, &nkb);
+    const uint32_t cta = blockIdx.x;
+    const WorkPlan plan = p.plan;
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < R; i++) { ptx::mbar_init(&raw_full[i], 1); ptx::mbar_init(&raw_empty[i], 4); }
-        for (int i = 0; i < SB; i++) { ptx::mbar_init(&b_full[i], 1); ptx::mbar_init(&b_empty[i], 1); }
-        for (int i = 0; i < SA; i++) { ptx::mbar_init(&a_full[i], 4); ptx::mbar_init(&a_empty[i], 1); }
-        ptx::mbar_init(acc_full, 1);
-        *abort_word = 0;
+    if ((ring & 1023u) != 0u) {   // uniform over the CTA: nothing has been set up yet
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrSmemAlign);
+        return;
+    }
+    if (warp == 1) {   // barrier set-up, one barrier per lane and round
+        for (int i = lane; i < R; i += 32) { ptx::mbar_init(full + 8 * i, kProducerWarps); ptx::mbar_init(w_empty + 8 * i, Cfg::readers); ptx::mbar_init(b_empty + 8 * i, 1); }
+        for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, 1); }
+        if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
+        if (lane == 0) *abort_word = 0;
         ptx::fence_barrier_init();
     }
-    if (warp == 2) {
-        ptx::tmem_alloc(tmem_holder, Budget<BW, N_TILE>::tmem_cols);
+    if (warp == 0) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTmemCols);
         ptx::tmem_relinquish();
     }
-    if (warp == 1 && lane == 0) ptx::prefetch_tensormap(&act_map);
+    if (warp == kProducerWarp && lane == 0) ptx::prefetch_tensormap(&act_map);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ packed-weight producer
+    if (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) {
+        // ------------------------------------------------------------ producers: warp 4 copies the activations and the
+        // weight segments of the tile's first 64-row block, warp 5 those of the second (one thread each)
         if (lane == 0) {
-            const uint64_t policy = ptx::policy_evict_first();
-            const uint64_t kblocks = K / kKBlock;
-            const uint64_t rb0 = (uint64_t)m_tile * 2;   // first 64-row block of this tile
-            const uint8_t* reg1 = weight + region_offset(BW, 1, M, K);
-            const uint8_t* reg2 = weight + region_offset(BW, 2, M, K);
-            const uint8_t* reg4 = weight + region_offset(BW, 4, M, K);
+            const uint32_t half = (uint32_t)(warp - kProducerWarp);
+            const uint64_t pol_w = ptx::policy_evict_first();
+            const uint64_t pol_b = ptx::policy_evict_last();
+            const uint64_t kblocks = plan.kblocks;
+            const uint8_t* reg1 = p.weight + region_offset(BW, 1, p.M, p.K);
+            const uint8_t* reg2 = p.weight + region_offset(BW, 2, p.M, p.K);
+            const uint8_t* reg4 = p.weight + region_offset(BW, 4, p.M, p.K);
+            ptx::RingPos<R> pos;
+            pos.set(0);
             uint32_t issued = 0;
-            for (uint32_t it = 0; it < nkb; it++) {
-                const uint32_t r = it % R;
-                if (!ptx::mbar_wait(&raw_empty[r], ((it / R) & 1u) ^ 1u, abort_word, kErrRawEmpty)) break;
-                ptx::mbar_arrive_expect_tx(&raw_full[r], Raw::bytes);
-                uint8_t* dst = raw_ring + r * Raw::bytes;
-                const uint64_t kb = kb_begin + it;
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    const uint64_t tile = (rb0 + i) * kblocks + kb;
-                    if (Raw::seg1) ptx::bulk_g2s(dst + Raw::off1 + i * Raw::seg1, reg1 + tile * Raw::seg1, Raw::seg1, &raw_full[r], policy);
-                    if (Raw::seg2) ptx::bulk_g2s(dst + Raw::off2 + i * Raw::seg2, reg2 + tile * Raw::seg2, Raw::seg2, &raw_full[r], policy);
-                    if (Raw::seg4) ptx::bulk_g2s(dst + Raw::off4 + i * Raw::seg4, reg4 + tile * Raw::seg4, Raw::seg4, &raw_full[r], policy);
+            bool ok = true;
+            SegmentIter iter;
+            Segment seg;
+            PROF_DECL
+            plan_start(plan, cta, &iter);
+            while (ok && plan_next(plan, cta, &iter, &seg)) {
+                const uint64_t blk0 = ((uint64_t)(seg.tile / plan.n_tiles) * 2 + half) * kblocks + seg.kb_begin;   // my row block, first K block
+                const int32_t n0 = (int32_t)((seg.tile % plan.n_tiles) * N_TILE);
+                const uint32_t nstages = (seg.nkb + KS - 1) / KS;
+                uint32_t sidx = plan_first_stage(cta, nstages);   // stage of the segment's K range handled next
+                for (uint32_t i = 0; i < nstages; i++) {
+                    const uint32_t kb_off = sidx * KS;
+                    const uint32_t cnt = seg.nkb - kb_off < (uint32_t)KS ? seg.nkb - kb_off : (uint32_t)KS;
+                    sidx = sidx + 1 == nstages ? 0u : sidx + 1;
+                    const uint32_t par = pos.lap ^ 1u;
+                    if (kUnified) {
+                        if (!PROF_WAIT(0, ptx::mbar_wait(a_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
+                    } else {
+                        if (!PROF_WAIT(0, ptx::mbar_wait(w_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
+                        if (!PROF_WAIT(1, ptx::mbar_wait(b_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
+                    }
+                    PROF_COUNT(6)
+                    PROF_BEGIN(t_issue)
+                    const uint32_t bar = full + 8 * pos.idx;
+                    const uint32_t dst = ring + pos.idx * Cfg::stage_bytes;
+                    // the activation copy always brings KS blocks (blocks past K are zero-filled), the weight copies cnt
+                    if (half == 0) {
+#if defined(FPX_EXP) && (FPX_EXP & 8)
+                        ptx::mbar_arrive_expect_tx(bar, cnt * (Raw::bytes128 / 2));
+#else
+                        ptx::mbar_arrive_expect_tx(bar, KS * Cfg::b_block + cnt * (Raw::bytes128 / 2));
+                        ptx::tma_load_3d(dst, &act_map, 0, n0, (int32_t)(seg.kb_begin + kb_off), bar, pol_b);
+#endif
+                    } else {
+                        ptx::mbar_arrive_expect_tx(bar, cnt * (Raw::bytes128 / 2));
+                    }
+                    const uint64_t b0 = blk0 + kb_off;
+                    if (Raw::seg1) ptx::bulk_g2s(dst + Cfg::off1 + half * KS * Raw::seg1, reg1 + b0 * Raw::seg1, cnt * Raw::seg1, bar, pol_w);
+                    if (Raw::seg2) ptx::bulk_g2s(dst + Cfg::off2 + half * KS * Raw::seg2, reg2 + b0 * Raw::seg2, cnt * Raw::seg2, bar, pol_w);
+                    if (Raw::seg4) ptx::bulk_g2s(dst + Cfg::off4 + half * KS * Raw::seg4, reg4 + b0 * Raw::seg4, cnt * Raw::seg4, bar, pol_w);
+                    PROF_END(3, t_issue)
+                    pos.advance(1);
+                    issued++;
                 }
-                issued = it + 1;
             }
-            if (*abort_word != 0) {   // gave up somewhere: let this thread's own copies land before leaving
+            PROF_FLUSH();
+            if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
                 const uint32_t first = issued > (uint32_t)R ? issued - R : 0u;
-                for (uint32_t it = first; it < issued; it++)
-                    ptx::mbar_wait(&raw_full[it % R], (it / R) & 1u, abort_word, kErrRawFull, 50000000ull);
+                for (uint32_t t = first; t < issued; t++)
+                    ptx::mbar_wait(full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, 64, 50000000ull);
             }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ activation producer
-        if (lane == 0) {
-            const uint64_t policy = ptx::policy_evict_last();
-            uint32_t issued = 0;
-            for (uint32_t it = 0; it < nkb; it++) {
-                const uint32_t s = it % SB;
-                if (!ptx::mbar_wait(&b_empty[s], ((it / SB) & 1u) ^ 1u, abort_word, kErrBEmpty)) break;
-                ptx::mbar_arrive_expect_tx(&b_full[s], BS::bytes);
-                ptx::tma_load_2d(b_ring + s * BS::bytes, &act_map, (int32_t)((kb_begin + it) * kKBlock),
-                                 (int32_t)(n_tile * N_TILE), &b_full[s], policy);
-                issued = it + 1;
-            }
-            if (*abort_word != 0) {
-                const uint32_t first = issued > (uint32_t)SB ? issued - SB : 0u;
-                for (uint32_t it = first; it < issued; it++)
-                    ptx::mbar_wait(&b_full[it % SB], (it / SB) & 1u, abort_word, kErrBFull, 50000000ull);
-            }
-        }
-    } else if (warp == 2) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::idesc_f16_f32(kTileM, N_TILE);
-            const uint32_t d_tmem = tmem_base + kAccColBase;
-            for (uint32_t it = 0; it < nkb; it++) {
-                const uint32_t sa = it % SA, sb = it % SB;
-                if (!ptx::mbar_wait(&a_full[sa], (it / SA) & 1u, abort_word, kErrAFull)) break;
-                if (!ptx::mbar_wait(&b_full[sb], (it / SB) & 1u, abort_word, kErrBFull)) break;
-                ptx::tc_fence_after_sync();
-                const uint64_t b_desc = ptx::smem_desc_k_sw128(ptx::smem_u32(b_ring + sb * BS::bytes));
-                const uint32_t a_tmem = tmem_base + sa * kAColsPerStage;
-#pragma unroll
-                for (uint32_t kk = 0; kk < 4; kk++)   // four K=16 steps; B advances 32 bytes inside the swizzle row
-                    ptx::mma_f16_ts(d_tmem, a_tmem + kk * 8, b_desc + kk * 2, idesc, (it | kk) != 0u ? 1u : 0u);
-                ptx::tc_commit(&a_empty[sa]);
-                ptx::tc_commit(&b_empty[sb]);
-            }
-            ptx::tc_commit(acc_full);
-            if (*abort_word != 0)   // nobody will consume the accumulator: wait here so dealloc follows the MMAs
-                ptx::mbar_wait(acc_full, 0, abort_word, kErrAccFull, 50000000ull);
         }
         __syncwarp();
-    } else {
-        // ------------------------------------------------------------ unpack warps, then epilogue
-        const int q = warp & 3;                          // tensor-memory lane quadrant this warp may touch
-        const int pair = (warp - kFirstDequantWarp) >> 2;   // 0/1: which of the two warps of the quadrant
-        const int h = q & 1;                             // sub-blocks 2h, 2h+1 of the 64-row block
-        const int rb = q >> 1;                           // 64-row block inside the 128-row tile
-        const int g = lane >> 2;
-        const uint32_t row0 = m_tile * kTileM + 32u * q;
-
-        // per-row constant 2^bias * scale (exact in fp16 unless it overflows; then multiply in two steps,
-        // like the reference's MultScale, utils_parallel_dequant.cuh:30-42)
-        const __half bias_h = __ushort_as_half(bias_half_bits(E_BITS));
-        __half sc[2][2];
-        bool overflow = false;
-#pragma unroll
-        for (int kk = 0; kk < 2; kk++)
-#pragma unroll
-            for (int hr = 0; hr < 2; hr++) {
-                const __half s = scales[row0 + 16 * kk + 8 * hr + g];
-                const __half c = __hmul(s, bias_h);
-                overflow |= __hisinf(c) || __hisnan(c);
-                sc[kk][hr] = c;
-            }
-        const bool two_step = __any_sync(0xffffffffu, overflow);
-        __half2 c2[2][2];
-        if (two_step) {
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++) c2[kk][hr] = __half2half2(scales[row0 + 16 * kk + 8 * hr + g]);
-        } else {
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++) c2[kk][hr] = __half2half2(sc[kk][hr]);
-        }
-        const __half2 bias2 = __half2half2(bias_h);
-
+    } else if (warp < kMaxIssuers) {
+        // ------------------------------------------------------------ MMA issue + epilogue
+        // Per segment: lane 0 of the first NI warps issues the MMAs (issuer i takes the stages t = i mod NI and
+        // accumulates them in its own accumulator); then all four warps, one per tensor-memory lane quadrant,
+        // read the accumulators, add them and store the tile (lane = output channel, column = token).
+        constexpr uint32_t idesc = ptx::idesc_f16_f32(kTileM, N_TILE);
+        const uint32_t me = (uint32_t)warp;
+        const int q = warp & 3;
+        const uint64_t b_desc0 = ptx::smem_desc_k_sw128(ring);
+        uint32_t j0 = 0, nseg = 0;
         bool ok = true;
-        for (uint32_t it = pair; it < nkb; it += 2) {
-            const uint32_t r = it % R;
-            if (!ptx::mbar_wait(&raw_full[r], (it / R) & 1u, abort_word, kErrRawFull)) { ok = false; break; }
-            const uint32_t* raw = reinterpret_cast<const uint32_t*>(raw_ring + r * Raw::bytes);
-            uint32_t w4[4][2], w2[4], w1[4];
+        SegmentIter iter;
+        Segment seg;
+        PROF_DECL
+        plan_start(plan, cta, &iter);
+        while (ok && plan_next(plan, cta, &iter, &seg)) {
+            const uint32_t nstages = (seg.nkb + KS - 1) / KS;
+            if (me < (uint32_t)NI && lane == 0) {
+                if (!PROF_WAIT(2, ptx::mbar_wait(acc_empty, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty, 64))) ok = false;
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + Cfg::acc_col0 + me * Cfg::acc_stride;
+                ptx::RingPos<R> rp;
+                ptx::RingPos<SA> ap;
+                rp.set(j0 + me);
+                ap.set(j0 + me);
+                uint32_t sidx = plan_first_stage(cta, nstages) + me;          // stage of the segment's K range handled next
+                uint32_t accumulate = 0u;                                    // 0 only for the first MMA of the segment
+                for (uint32_t t = me; ok && t < nstages; t += NI) {
+                    while (sidx >= nstages) sidx -= nstages;
+                    const uint32_t cnt = seg.nkb - sidx * KS < (uint32_t)KS ? seg.nkb - sidx * KS : (uint32_t)KS;
+                    sidx += NI;
+                    if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull))) { ok = false; break; }
+                    // the activations of the stage landed before its weights were unpacked; this only makes them visible here
+                    if (!PROF_WAIT(1, ptx::mbar_wait(full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                    PROF_COUNT(6)
+                    PROF_BEGIN(t_issue)
+                    ptx::tc_fence_after_sync();
+                    const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::stage_bytes >> 4));
+                    const uint32_t a_tmem = tmem_base + ap.idx * Cfg::a_cols;
+#if !(defined(FPX_EXP) && (FPX_EXP & 4))
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                w4[j][0] = raw[Raw::off4 / 4 + rb * (Raw::seg4 / 4) + (j * 4 + 2 * h + 0) * 32 + lane];
-                w4[j][1] = raw[Raw::off4 / 4 + rb * (Raw::seg4 / 4) + (j * 4 + 2 * h + 1) * 32 + lane];
-                w2[j] = Raw::seg2 ? raw[Raw::off2 / 4 + rb * (Raw::seg2 / 4) + (j * 2 + h) * 32 + lane] : 0u;
-                w1[j] = Raw::seg1 ? raw[Raw::off1 / 4 + rb * (Raw::seg1 / 4) + j * 32 + lane] : 0u;
-            }
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&raw_empty[r]);   // the slot can be refilled while we compute
-
-            uint32_t v[2][16];
+                    for (uint32_t kbi = 0; kbi < (uint32_t)KS; kbi++)
+                        if (kbi < cnt) {
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                uint32_t pat[8];
-                unpack16<E_BITS>(w4[j][0], w4[j][1], w2[j], w1[j], h, pat);
-#pragma unroll
-                for (int kk = 0; kk < 2; kk++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        uint32_t x = pat[4 * kk + i];
-                        if (two_step) x = scale_pair(x, bias2);
-                        v[kk][4 * j + i] = scale_pair(x, c2[kk][i & 1]);   // a0,a2: row g; a1,a3: row g+8
-                    }
-            }
-            const uint32_t sa = it % SA;
-            if (!ptx::mbar_wait(&a_empty[sa], ((it / SA) & 1u) ^ 1u, abort_word, kErrAEmpty)) { ok = false; break; }
-            ptx::tc_fence_after_sync();
-            const uint32_t a_addr = tmem_base + ((uint32_t)(32 * q) << 16) + sa * kAColsPerStage;
-            ptx::tmem_st_16x128b_x8(a_addr, v[0]);
-            ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), v[1]);
-            ptx::tc_wait_st();
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&a_full[sa]);
-        }
-
-        // -------- epilogue: tensor-memory lane = output channel, column = token
-        if (ok && nkb > 0) ok = ptx::mbar_wait(acc_full, 0, abort_word, kErrAccFull);
-        ptx::tc_fence_after_sync();
-        if (ok && *abort_word == 0) {
-            const uint32_t row = row0 + lane;
-            constexpr int kColsPerWarp = N_TILE / 2;
-#pragma unroll 1
-            for (int c0 = pair * kColsPerWarp; c0 < (pair + 1) * kColsPerWarp; c0 += 8) {
-                const uint32_t n0 = n_tile * N_TILE + c0;
-                if (n0 >= N) break;
-                uint32_t acc[8];
-                if (nkb > 0) {
-                    ptx::tmem_ld_32x32b_x8(tmem_base + ((uint32_t)(32 * q) << 16) + kAccColBase + c0, acc);
-                    ptx::tc_wait_ld();
-                } else {
-#pragma unroll
-                    for (int u = 0; u < 8; u++) acc[u] = 0u;
+                            for (uint32_t kk = 0; kk < 4; kk++) {   // four K=16 steps; B advances 32 bytes inside the swizzle row
+                                ptx::mma_f16_ts(d_tmem, a_tmem + kbi * kAColsPerKBlock + kk * 8,
+                                                b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
+                                accumulate = 1u;
+                            }
+                        }
+#endif
+                    PROF_END(3, t_issue)
+                    PROF_BEGIN(t_commit)
+                    ptx::tc_commit(a_empty + 8 * ap.idx);
+                    if (!kUnified) ptx::tc_commit(b_empty + 8 * rp.idx);
+                    PROF_END(4, t_commit)
+                    rp.advance(NI);
+                    ap.advance(NI);
                 }
+                if (ok) {
+                    if (me < nstages) ptx::tc_commit(acc_full);   // arrives once this issuer's MMAs are done
+                    else ptx::mbar_arrive(acc_full);              // nothing to add to this segment
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            j0 += nstages;
+
+            const uint32_t m_tile = seg.tile / plan.n_tiles, n_tile = seg.tile % plan.n_tiles;
+            const uint32_t row_in_tile = 32u * q + lane;
+            const uint32_t row = m_tile * kTileM + row_in_tile;
+#ifdef FPX_EPI_SCALE
+            const float row_scale = __half2float(p.scales[row]) * (float)(1u << (16 - (1 << (E_BITS - 1))));
+#else
+            const float row_scale = 1.0f;
+#endif
+            if (!PROF_WAIT(5, ptx::mbar_wait(acc_full, nseg & 1u, abort_word, kErrAccFull, 64))) { ok = false; break; }
+            ptx::tc_fence_after_sync();
+            const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::acc_col0;
+            const uint32_t parts = nstages < (uint32_t)NI ? nstages : (uint32_t)NI;   // issuers that contributed
+#pragma unroll 1
+            for (int c0 = 0; c0 < N_TILE; c0 += 8) {
+                const uint32_t n0 = n_tile * N_TILE + c0;
+                if (n0 >= p.N) break;
+                uint32_t v[8];
+                ptx::tmem_ld_32x32b_x8(acc + c0, v);
+                ptx::tc_wait_ld();
+                float f[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) f[u] = __uint_as_float(v[u]);
+#pragma unroll
+                for (uint32_t i = 1; i < (uint32_t)NI; i++)
+                    if (i < parts) {
+                        ptx::tmem_ld_32x32b_x8(acc + i * Cfg::acc_stride + c0, v);
+                        ptx::tc_wait_ld();
+#pragma unroll
+                        for (int u = 0; u < 8; u++) f[u] += __uint_as_float(v[u]);
+                    }
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
                     const uint32_t n = n0 + u;
-                    if (n < N) {
-                        const float f = __uint_as_float(acc[u]);
-                        if (PARTIAL)
-                            reinterpret_cast<float*>(out)[((size_t)z * N + n) * M + row] = f;
+                    if (n < p.N) {
+                        const float val = f[u] * row_scale;
+                        if (seg.out_kind == kOutDirect)
+                            p.out[(size_t)n * p.M + row] = __float2half_rn(val);
+                        else if (seg.out_kind == kOutSplitPartial)
+                            p.workspace[((size_t)seg.out_index * p.N + n) * p.M + row] = val;
                         else
-                            reinterpret_cast<__half*>(out)[(size_t)n * M + row] = __float2half_rn(f);
+                            p.workspace[((size_t)seg.out_index * N_TILE + (c0 + u)) * kTileM + row_in_tile] = val;
                     }
                 }
             }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty);
+            nseg++;
         }
+        PROF_FLUSH();
+    } else if (warp >= kFirstDequantWarp) {
+        // ------------------------------------------------------------ unpack warps
+        const int q = warp & 3;                                   // tensor-memory lane quadrant this warp may touch
+        const uint32_t group = (uint32_t)(warp - kFirstDequantWarp) >> 2;
+        constexpr uint32_t kStageGroups = kDequantGroups / KS;   // groups that take turns on consecutive stages
+        const uint32_t kbi = group % KS;                         // K block of the stage this warp unpacks
+        const uint32_t turn = group / KS;                        // it takes the stages j with j % kStageGroups == turn
+        const int h = q & 1;                                      // sub-blocks 2h, 2h+1 of the 64-row block
+        const int rb = q >> 1;                                    // 64-row block inside the 128-row tile
+        const int g = lane >> 2;
+        const uint32_t lane_base = ring + 4u * lane;
+        const uint32_t o4 = Cfg::off4 + (rb * KS + kbi) * Raw::seg4 + 2 * h * 128;
+        const uint32_t o2 = Cfg::off2 + (rb * KS + kbi) * Raw::seg2 + h * 128;
+        const uint32_t o1 = Cfg::off1 + (rb * KS + kbi) * Raw::seg1;
+        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * q) << 16) + kbi * kAColsPerKBlock;
+        uint32_t j0 = 0;   // running stage index at the start of the segment
+        bool ok = true;
+        SegmentIter iter;
+        Segment seg;
+        PROF_DECL
+        plan_start(plan, cta, &iter);
+        while (ok && plan_next(plan, cta, &iter, &seg)) {
+#ifndef FPX_EPI_SCALE
+            // per-row constant 2^bias * scale (exact in fp16 unless it overflows; then multiply in two steps,
+            // like the reference's MultScale, utils_parallel_dequant.cuh:30-42)
+            const __half bias_h = __ushort_as_half(bias_half_bits(E_BITS));
+            const __half2 bias2 = __half2half2(bias_h);
+            const uint32_t row0 = (seg.tile / plan.n_tiles) * kTileM + 32u * q;
+            __half2 c2[2][2];
+            bool overflow = false;
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++)
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++) {
+                    const __half s = p.scales[row0 + 16 * kk + 8 * hr + g];
+                    const __half c = __hmul(s, bias_h);
+                    overflow |= __hisinf(c) || __hisnan(c);
+                    c2[kk][hr] = __halves2half2(c, s);    // low: folded constant, high: plain scale
+                }
+            const bool two_step = __any_sync(0xffffffffu, overflow);
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++)
+#pragma unroll
+                for (int hr = 0; hr < 2; hr++)
+                    c2[kk][hr] = two_step ? __half2half2(__high2half(c2[kk][hr])) : __half2half2(__low2half(c2[kk][hr]));
+#else
+            (void)g;
+#endif
+            const uint32_t nstages = (seg.nkb + KS - 1) / KS;
+            // this warp's first stage of the segment
+            uint32_t t = (turn + kStageGroups - (j0 % kStageGroups)) % kStageGroups;
+            ptx::RingPos<R> rp;
+            ptx::RingPos<SA> ap;
+            rp.set(j0 + t);
+            ap.set(j0 + t);
+            uint32_t sidx = plan_first_stage(cta, nstages) + t;   // stage of the segment's K range handled next
+            for (; t < nstages; t += kStageGroups) {
+                while (sidx >= nstages) sidx -= nstages;
+                const bool valid = sidx * KS + kbi < seg.nkb;    // the last stage of the K range may hold fewer K blocks
+                sidx += kStageGroups;
+                if (!PROF_WAIT(0, ptx::mbar_wait(full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                PROF_COUNT(6)
+                PROF_BEGIN(t_math)
+                uint32_t v[2][16];
+                if (valid) {
+                    const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
+                    uint32_t w4[4][2], w2[4], w1[4];
+#pragma unroll
+                    for (int jj = 0; jj < 4; jj++) {
+#if defined(FPX_EXP) && (FPX_EXP & 32)
+                        w4[jj][0] = raw + jj; w4[jj][1] = raw - jj; w2[jj] = raw * 3; w1[jj] = raw * 5;
+                        continue;
+#endif
+                        w4[jj][0] = ptx::lds_u32(raw + o4 + (jj * 4 + 0) * 128);
+                        w4[jj][1] = ptx::lds_u32(raw + o4 + (jj * 4 + 1) * 128);
+                        w2[jj] = Raw::seg2 ? ptx::lds_u32(raw + o2 + (jj * 2) * 128) : 0u;
+                        w1[jj] = Raw::seg1 ? ptx::lds_u32(raw + o1 + jj * 128) : 0u;
+                    }
+                    if (!kUnified) {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);   // the weights can be refilled while we compute
+                    }
+#if defined(FPX_EXP) && (FPX_EXP & 1)
+#pragma unroll
+                    for (int jj = 0; jj < 4; jj++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) { v[0][4 * jj + i] = w4[jj][0] + i + w2[jj]; v[1][4 * jj + i] = w4[jj][1] + i + w1[jj]; }
+#else
+#pragma unroll
+                    for (int jj = 0; jj < 4; jj++) {
+                        uint32_t pat[8];
+                        unpack16<E_BITS>(w4[jj][0], w4[jj][1], w2[jj], w1[jj], h, pat);
+#pragma unroll
+                        for (int kk = 0; kk < 2; kk++)
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+#ifndef FPX_EPI_SCALE
+                                uint32_t x = pat[4 * kk + i];
+                                if (two_step) x = scale_pair(x, bias2);
+                                v[kk][4 * jj + i] = scale_pair(x, c2[kk][i & 1]);   // a0,a2: row g; a1,a3: row g+8
+#else
+                                v[kk][4 * jj + i] = pat[4 * kk + i];
+#endif
+                            }
+                    }
+#endif
+                } else if (!kUnified) {
+                    if (lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);
+                }
+                PROF_END(1, t_math)
+                if (!PROF_WAIT(2, ptx::mbar_wait(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                PROF_BEGIN(t_st)
+                if (valid) {
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = a_lane + ap.idx * Cfg::a_cols;
+#if defined(FPX_EXP) && (FPX_EXP & 2)
+                    if (v[0][0] == 0x12345u && v[1][3] == 0x777u) ptx::tmem_st_16x128b_x8(a_addr, v[0]);
+#else
+                    ptx::tmem_st_16x128b_x8(a_addr, v[0]);
+                    ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), v[1]);
+                    ptx::tc_wait_st();
+#endif
+                    ptx::tc_fence_before_sync();
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(a_full + 8 * ap.idx);
+                PROF_END(3, t_st)
+                rp.advance(kStageGroups);
+                ap.advance(kStageGroups);
+            }
+            j0 += nstages;
+        }
+        PROF_FLUSH();
     }
 
     // ------------------------------------------------------------ teardown
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 2) {
+    if (warp == 0) {
+        if (*abort_word != 0 && lane == 0) {   // gave up: let MMAs that may still be in flight finish before freeing
+            const uint64_t t0 = ptx::global_timer_ns();
+            while (ptx::global_timer_ns() - t0 < 2000000ull) { }
+        }
+        __syncwarp();
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, Budget<BW, N_TILE>::tmem_cols);
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
-    if (threadIdx.x == 0 && *abort_word != 0) atomicCAS(status, 0, *abort_word);
+    if (threadIdx.x == 0 && *abort_word != 0) atomicCAS(p.status, 0, *abort_word);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -336,14 +531,60 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
     if (i >= elems) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < split_k; s++) {
-        const float4 p = *reinterpret_cast<const float4*>(partials + (size_t)s * elems + i);
-        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        const float4 v = *reinterpret_cast<const float4*>(partials + (size_t)s * elems + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
     uint2 packed;
     packed.x = *reinterpret_cast<uint32_t*>(&lo);
     packed.y = *reinterpret_cast<uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(out + i) = packed;
+}
+
+// Fix-up of the stream-K remainder: CTA = (remainder tile, token column), thread = output channel.  Sums, in CTA
+// order, the partial slots of every CTA that worked on the tile (fp32) and stores fp16; tiles that one CTA
+// computed alone were stored directly and are skipped.  Four running sums keep several loads in flight.
+__global__ void __launch_bounds__(kTileM) streamk_fixup_kernel(__half* __restrict__ out, const float* __restrict__ slots,
+                                                               uint32_t M, uint32_t N, int n_tile_size, WorkPlan plan) {
+    __shared__ uint32_t cand_slot[2 * kTileM];   // per candidate CTA: its slot, or ~0u when it holds nothing
+    __shared__ uint32_t part_slot[2 * kTileM];   // slots that hold a part of this tile, in CTA order
+    __shared__ uint32_t part_count;
+    const uint32_t r = blockIdx.x, c = blockIdx.y;
+    uint32_t first, last;
+    plan_tile_owners(plan, r, &first, &last);
+    if (first == last) return;
+    const uint32_t tile = plan_full_waves(plan) * plan.grid + r;
+    const uint32_t m_tile = tile / plan.n_tiles, n_tile = tile % plan.n_tiles;
+    const uint32_t n = n_tile * n_tile_size + c;
+    if (n >= N) return;
+    const uint32_t span = last - first + 1 < 2u * kTileM ? last - first + 1 : 2u * kTileM;
+    for (uint32_t i = threadIdx.x; i < span; i += kTileM) {   // one candidate CTA per thread
+        const uint32_t cta = first + i;
+        const bool holds = plan_rem_begin(plan, cta) != plan_rem_begin(plan, cta + 1);
+        cand_slot[i] = holds ? plan_tile_slot(plan, r, cta) : ~0u;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t cnt = 0;
+        for (uint32_t i = 0; i < span; i++)
+            if (cand_slot[i] != ~0u) part_slot[cnt++] = cand_slot[i];
+        part_count = cnt;
+    }
+    __syncthreads();
+    const uint32_t row = threadIdx.x;
+    const uint32_t count = part_count;
+    const float* base = slots + (size_t)c * kTileM + row;
+    const size_t slot_stride = (size_t)n_tile_size * kTileM;
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    uint32_t i = 0;
+    for (; i + 4 <= count; i += 4) {
+        acc0 += base[part_slot[i] * slot_stride];
+        acc1 += base[part_slot[i + 1] * slot_stride];
+        acc2 += base[part_slot[i + 2] * slot_stride];
+        acc3 += base[part_slot[i + 3] * slot_stride];
+    }
+    for (; i < count; i++) acc0 += base[part_slot[i] * slot_stride];
+    out[(size_t)n * M + m_tile * kTileM + row] = __float2half_rn((acc0 + acc1) + (acc2 + acc3));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -353,35 +594,36 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void* p = nullptr;
+        void* ptr = nullptr;
         cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
             q != cudaDriverEntryPointSuccess)
             return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
+        return reinterpret_cast<EncodeTiledFn>(ptr);
     }();
     return fn;
 }
 
-// Tensor map over the activations [N rows][K fp16], box = 64 K x n_tile rows, 128-byte swizzle.
-cudaError_t make_act_map(CUtensorMap* map, const __half* act, size_t N, size_t K, int n_tile) {
+// Tensor map over the activations [N rows][K fp16] seen as (64 K, N rows, K/64 blocks): one copy of box
+// (64, n_tile, ks) lands ks consecutive [n_tile x 128 B] blocks, each 128-byte swizzled, rows past N and blocks
+// past K zero-filled.
+cudaError_t make_act_map(CUtensorMap* map, const __half* act, size_t N, size_t K, int n_tile, int ks) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return cudaErrorNotSupported;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
-    cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
-    cuuint32_t box[2] = {(cuuint32_t)kKBlock, (cuuint32_t)n_tile};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(act), dims, strides, box, estr,
+    cuuint64_t dims[3] = {(cuuint64_t)kKBlock, (cuuint64_t)N, (cuuint64_t)(K / kKBlock)};
+    cuuint64_t strides[2] = {(cuuint64_t)K * sizeof(__half), (cuuint64_t)kKBlock * sizeof(__half)};
+    cuuint32_t box[3] = {(cuuint32_t)kKBlock, (cuuint32_t)n_tile, (cuuint32_t)ks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(act), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int BW, int N_TILE, bool PARTIAL>
-cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const uint8_t* weight, const __half* scales,
-                       void* out, size_t M, size_t N, size_t K, int split_k, int* status) {
-    auto kernel = fpx_gemm_kernel<BW, N_TILE, PARTIAL>;
-    constexpr uint32_t smem = Budget<BW, N_TILE>::smem_bytes;
+template <int BW, int N_TILE>
+cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
+    auto kernel = fpx_gemm_kernel<BW, N_TILE>;
+    constexpr uint32_t smem = Config<BW, N_TILE>::smem_bytes;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
@@ -391,29 +633,47 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const uint8_
         if (err != cudaSuccess) return err;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    dim3 grid((unsigned)(M / kTileM), (unsigned)((N + N_TILE - 1) / N_TILE), (unsigned)split_k);
-    kernel<<<grid, kThreads, smem, stream>>>(map, weight, scales, out, (uint32_t)M, (uint32_t)N, (uint32_t)K,
-                                             (uint32_t)split_k, status);
+    kernel<<<prm.plan.grid, kThreads, smem, stream>>>(map, prm);
     return cudaGetLastError();
 }
 
-template <int BW, bool PARTIAL>
-cudaError_t launch_by_n(int n_tile, cudaStream_t stream, const CUtensorMap& map, const uint8_t* weight,
-                        const __half* scales, void* out, size_t M, size_t N, size_t K, int split_k, int* status) {
+template <int BW>
+cudaError_t launch_by_n(int n_tile, cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
     switch (n_tile) {
-        case 16:  return launch_one<BW, 16, PARTIAL>(stream, map, weight, scales, out, M, N, K, split_k, status);
-        case 32:  return launch_one<BW, 32, PARTIAL>(stream, map, weight, scales, out, M, N, K, split_k, status);
-        case 64:  return launch_one<BW, 64, PARTIAL>(stream, map, weight, scales, out, M, N, K, split_k, status);
-        case 128: return launch_one<BW, 128, PARTIAL>(stream, map, weight, scales, out, M, N, K, split_k, status);
-        default:  return launch_one<BW, 256, PARTIAL>(stream, map, weight, scales, out, M, N, K, split_k, status);
+        case 16:  return launch_one<BW, 16>(stream, map, prm);
+        case 32:  return launch_one<BW, 32>(stream, map, prm);
+        case 64:  return launch_one<BW, 64>(stream, map, prm);
+        case 128: return launch_one<BW, 128>(stream, map, prm);
+        default:  return launch_one<BW, 256>(stream, map, prm);
     }
 }
 
 }  // namespace
 
+#ifdef FPX_PROFILE
+extern "C" int fp6b200_debug_read_profile(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_prof, sizeof(g_prof));
+}
+#endif
+
+int device_sm_count() {
+    static int counts[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!counts[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        counts[dev] = n;
+    }
+    return counts[dev];
+}
+
 int gemm_n_tile(size_t N) { return N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256))); }
 
-int gemm_ctas_per_sm(int n_tile) { return n_tile <= 64 ? 2 : 1; }
+size_t gemm_auto_workspace_bytes(size_t N) {
+    // stream-K: two partial slots of 128 x n_tile fp32 per CTA
+    return (size_t)2 * device_sm_count() * kTileM * gemm_n_tile(N) * sizeof(float);
+}
 
 cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k) {
     const size_t threads = (elems + 3) / 4;
@@ -425,28 +685,59 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
                         int* status) {
     if (!format_supported(e_bits, m_bits)) return cudaErrorInvalidValue;
-    if (M == 0 || M % 256 != 0 || K == 0 || K % 64 != 0 || N == 0 || split_k < 1 || split_k > 65535)
+    if (M == 0 || M % 256 != 0 || K == 0 || K % 64 != 0 || N == 0 || split_k < 0 || split_k > 65535)
         return cudaErrorInvalidValue;
-    if (!weight || !scales || !act || !out || (split_k > 1 && !workspace)) return cudaErrorInvalidValue;
+    if (!weight || !scales || !act || !out || (split_k != 1 && !workspace)) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(weight) & 15) || (reinterpret_cast<uintptr_t>(act) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 7) || (reinterpret_cast<uintptr_t>(workspace) & 15))
         return cudaErrorMisalignedAddress;
-    if (M > 0xffffffffull || N > 0x7fffffffull || K > 0x7fffffffull) return cudaErrorInvalidValue;
+    if (M > 0x7fffffffull || N > 0x7fffffffull || K > 0x7fffffffull) return cudaErrorInvalidValue;
     const int n_tile = gemm_n_tile(N);
-    if ((N + n_tile - 1) / n_tile > 65535) return cudaErrorInvalidValue;
+    const size_t n_tiles = (N + n_tile - 1) / n_tile;
+    if ((M / kTileM) * n_tiles > 0x3fffffffull) return cudaErrorInvalidValue;
     CUtensorMap map;
-    cudaError_t err = make_act_map(&map, act, N, K, n_tile);
+    cudaError_t err = make_act_map(&map, act, N, K, n_tile, n_tile <= 128 ? 2 : 1);
     if (err != cudaSuccess) return err;
-    const uint8_t* w = static_cast<const uint8_t*>(weight);
-    const int bw = 1 + e_bits + m_bits;
-    if (split_k == 1) {
-        return bw == 6 ? launch_by_n<6, false>(n_tile, stream, map, w, scales, out, M, N, K, 1, status)
-                       : launch_by_n<5, false>(n_tile, stream, map, w, scales, out, M, N, K, 1, status);
+
+    const int sms = device_sm_count();
+    Params prm;
+    prm.weight = static_cast<const uint8_t*>(weight);
+    prm.scales = scales;
+    prm.out = out;
+    prm.workspace = workspace;
+    prm.M = (uint32_t)M;
+    prm.N = (uint32_t)N;
+    prm.K = (uint32_t)K;
+    prm.status = status;
+    WorkPlan& plan = prm.plan;
+    plan.m_tiles = (uint32_t)(M / kTileM);
+    plan.n_tiles = (uint32_t)n_tiles;
+    plan.kblocks = (uint32_t)(K / kKBlock);
+    const uint64_t tiles = (uint64_t)plan.m_tiles * plan.n_tiles;
+    int eff_split = 1;
+    if (split_k == 0) {   // the library's own decomposition: data-parallel waves + stream-K remainder
+        plan.mode = kStreamK;
+        plan.split_k = 1;
+        const uint64_t units = tiles * plan.kblocks;
+        plan.grid = (uint32_t)(units < (uint64_t)sms ? units : (uint64_t)sms);
+    } else {              // the caller's split: splits beyond the number of K blocks would be empty
+        plan.mode = kClassic;
+        eff_split = split_k < (int)plan.kblocks ? split_k : (int)plan.kblocks;
+        plan.split_k = (uint32_t)eff_split;
+        const uint64_t items = tiles * eff_split;
+        plan.grid = (uint32_t)(items < (uint64_t)sms ? items : (uint64_t)sms);
     }
-    err = bw == 6 ? launch_by_n<6, true>(n_tile, stream, map, w, scales, workspace, M, N, K, split_k, status)
-                  : launch_by_n<5, true>(n_tile, stream, map, w, scales, workspace, M, N, K, split_k, status);
+    const int bw = 1 + e_bits + m_bits;
+    err = bw == 6 ? launch_by_n<6>(n_tile, stream, map, prm) : launch_by_n<5>(n_tile, stream, map, prm);
     if (err != cudaSuccess) return err;
-    return launch_splitk_reduce(stream, out, workspace, M * N, split_k);
+    if (plan.mode == kStreamK) {
+        const uint32_t rem = plan_rem_tiles(plan);
+        if (rem == 0) return cudaSuccess;
+        streamk_fixup_kernel<<<dim3(rem, (unsigned)n_tile), kTileM, 0, stream>>>(out, workspace, (uint32_t)M, (uint32_t)N, n_tile, plan);
+        return cudaGetLastError();
+    }
+    if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split);
+    return cudaSuccess;
 }
 
 }  // namespace fpx

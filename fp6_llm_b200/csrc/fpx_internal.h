@@ -16,7 +16,9 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
                         int* status);
 cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k);
 int gemm_n_tile(size_t N);
-int gemm_ctas_per_sm(int n_tile);
+int device_sm_count();
+// Workspace the GEMM needs when it picks its own decomposition (split_k == 0).
+size_t gemm_auto_workspace_bytes(size_t N);
 
 // Weight format kernels.  All pointers are device pointers; in != out.
 cudaError_t launch_prepack(int e_bits, int m_bits, cudaStream_t stream, const void* unpacked, void* packed, size_t M,

@@ -161,4 +161,128 @@ FPX_HD void split_range(uint32_t k_blocks, uint32_t splits, uint32_t z, uint32_t
     *begin = z * base + (z < extra ? z : extra);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Work decomposition of the persistent GEMM kernel.
+//
+// An output tile is 128 rows x n_tile columns; a *unit* is one 64-wide K block of one tile.  `grid`
+// CTAs each walk a list of *segments* (tile, first K block, number of K blocks):
+//   kClassic  the caller fixed split_k: item i = (tile i / split_k, split i % split_k), CTA c takes
+//             items c, c + grid, ...; a split writes an fp32 partial [split][N][M] that a reduction
+//             kernel sums (the reference's scheme, fp6_llm/csrc/fp6_linear.cu:81-99).
+//   kStreamK  whole waves of tiles are taken data-parallel (CTA c takes tiles c, c + grid, ...), then
+//             the units of the remaining tiles are dealt out evenly: CTA c gets units
+//             [c*U/grid, (c+1)*U/grid) of the remainder.  A CTA's first and last remainder segment may
+//             cover only part of a tile's K range; those go to partial slots 2c and 2c+1 and a fix-up
+//             kernel sums the slots of every split tile in CTA order.
+enum WorkMode : uint32_t { kClassic = 0, kStreamK = 1 };
+enum OutKind : uint32_t { kOutDirect = 0, kOutSplitPartial = 1, kOutSlotPartial = 2 };
+
+struct WorkPlan {
+    uint32_t mode;
+    uint32_t m_tiles;     // M / 128
+    uint32_t n_tiles;     // ceil(N / n_tile)
+    uint32_t kblocks;     // K / 64
+    uint32_t split_k;     // kClassic only (1 <= split_k <= kblocks)
+    uint32_t grid;        // number of CTAs
+};
+
+struct Segment {
+    uint32_t tile;        // m_tile * n_tiles + n_tile
+    uint32_t kb_begin;
+    uint32_t nkb;         // > 0
+    uint32_t out_kind;
+    uint32_t out_index;   // split index (kOutSplitPartial) or slot (kOutSlotPartial)
+};
+
+FPX_HD uint32_t plan_tiles(const WorkPlan& p) { return p.m_tiles * p.n_tiles; }
+FPX_HD uint32_t plan_full_waves(const WorkPlan& p) { return plan_tiles(p) / p.grid; }
+FPX_HD uint32_t plan_rem_tiles(const WorkPlan& p) { return plan_tiles(p) - plan_full_waves(p) * p.grid; }
+// first remainder unit of CTA c (kStreamK); c == grid gives the total
+FPX_HD uint64_t plan_rem_begin(const WorkPlan& p, uint32_t c) {
+    return (uint64_t)c * ((uint64_t)plan_rem_tiles(p) * p.kblocks) / p.grid;
+}
+// CTA that owns remainder unit u
+FPX_HD uint32_t plan_rem_owner(const WorkPlan& p, uint64_t u) {
+    const uint64_t total = (uint64_t)plan_rem_tiles(p) * p.kblocks;
+    return (uint32_t)(((u + 1) * p.grid - 1) / total);
+}
+
+struct SegmentIter {
+    uint32_t step;        // segments handed out so far
+    uint64_t cur, end;    // remainder units still to hand out (kStreamK)
+    uint32_t rem_first;   // 1 until the first remainder segment has been handed out
+};
+
+FPX_HD void plan_start(const WorkPlan& p, uint32_t cta, SegmentIter* it) {
+    it->step = 0;
+    it->rem_first = 1;
+    if (p.mode == kStreamK) {
+        it->cur = plan_rem_begin(p, cta);
+        it->end = plan_rem_begin(p, cta + 1);
+    } else {
+        it->cur = it->end = 0;
+    }
+}
+
+// Next segment of CTA `cta`; false when the CTA is done.  Every role of the CTA calls this with its own
+// iterator and sees the same sequence.
+FPX_HD bool plan_next(const WorkPlan& p, uint32_t cta, SegmentIter* it, Segment* seg) {
+    if (p.mode == kClassic) {
+        const uint64_t item = (uint64_t)cta + (uint64_t)it->step * p.grid;
+        if (item >= (uint64_t)plan_tiles(p) * p.split_k) return false;
+        it->step++;
+        seg->tile = (uint32_t)(item / p.split_k);
+        seg->out_index = (uint32_t)(item % p.split_k);
+        split_range(p.kblocks, p.split_k, seg->out_index, &seg->kb_begin, &seg->nkb);
+        seg->out_kind = p.split_k > 1 ? kOutSplitPartial : kOutDirect;
+        return true;
+    }
+    const uint32_t waves = plan_full_waves(p);
+    if (it->step < waves) {
+        seg->tile = cta + it->step * p.grid;
+        seg->kb_begin = 0;
+        seg->nkb = p.kblocks;
+        seg->out_kind = kOutDirect;
+        seg->out_index = 0;
+        it->step++;
+        return true;
+    }
+    if (it->cur >= it->end) return false;
+    const uint32_t kb = (uint32_t)(it->cur % p.kblocks);
+    const uint64_t left = it->end - it->cur;
+    const uint32_t n = (uint32_t)(left < (uint64_t)(p.kblocks - kb) ? left : (uint64_t)(p.kblocks - kb));
+    seg->tile = waves * p.grid + (uint32_t)(it->cur / p.kblocks);
+    seg->kb_begin = kb;
+    seg->nkb = n;
+    if (n == p.kblocks) {
+        seg->out_kind = kOutDirect;
+        seg->out_index = 0;
+    } else {
+        seg->out_kind = kOutSlotPartial;
+        seg->out_index = 2 * cta + (it->rem_first ? 0u : 1u);
+    }
+    it->rem_first = 0;
+    it->cur += n;
+    it->step++;
+    return true;
+}
+
+// All CTAs would otherwise walk K in lockstep and ask the same L2 lines for the same activation block at
+// the same time.  Each CTA therefore starts a segment at its own stage and wraps around (the order of the
+// K blocks does not matter for the sum): the i-th stage processed is stage (first + i) mod nstages.
+FPX_HD uint32_t plan_first_stage(uint32_t cta, uint32_t nstages) { return (cta * 7u) % nstages; }
+
+// Fix-up side: for remainder tile r (0 <= r < plan_rem_tiles) the CTAs [*first, *last] hold its parts;
+// *first == *last means one CTA computed the whole tile and stored it directly.
+FPX_HD void plan_tile_owners(const WorkPlan& p, uint32_t r, uint32_t* first, uint32_t* last) {
+    *first = plan_rem_owner(p, (uint64_t)r * p.kblocks);
+    *last = plan_rem_owner(p, (uint64_t)(r + 1) * p.kblocks - 1);
+}
+// Slot in which CTA c left its part of remainder tile r (c in [first, last], first != last).  CTAs in
+// that range whose unit range is empty (plan_rem_begin(c) == plan_rem_begin(c+1)) hold nothing.
+FPX_HD uint32_t plan_tile_slot(const WorkPlan& p, uint32_t r, uint32_t c) {
+    const uint64_t begin = plan_rem_begin(p, c);
+    return (begin / p.kblocks == r) ? 2 * c : 2 * c + 1;
+}
+
 }  // namespace fpx

@@ -18,20 +18,20 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // ------------------------------------------------------------------ mbarrier
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+// Barriers are addressed by their 32-bit shared-space address (smem_u32 of the uint64_t).
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
@@ -40,28 +40,51 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
 
 // Bounded wait.  Returns false when the CTA-wide abort word is (or becomes) non-zero: either another
 // thread gave up, or this wait itself ran past `timeout_ns`, in which case it records `code` there.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code,
-                                          uint64_t timeout_ns = 2000000000ull) {
+// Between polls the thread sleeps `sleep_ns` so that waiting warps do not flood the shared-memory pipe
+// that the copy and MMA issuing threads also need; the clock is only consulted every 256 polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int code,
+                                          uint32_t sleep_ns = 32, uint64_t timeout_ns = 2000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    uint64_t t0 = 0;
     uint32_t spins = 0;
+#pragma unroll 1
     for (;;) {
+        __nanosleep(sleep_ns);
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 31u) == 0u) {
+        if ((++spins & 255u) == 0u) {
             if (*abort_word != 0) return false;
-            if (global_timer_ns() - t0 > timeout_ns) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > timeout_ns) {
                 *abort_word = code;
                 return false;
             }
         }
     }
+}
+
+// Position in a ring of SIZE slots: slot index and the parity of the number of completed laps.
+template <int SIZE>
+struct RingPos {
+    uint32_t idx, lap;
+    __device__ __forceinline__ void set(uint32_t n) { idx = n % SIZE; lap = (n / SIZE) & 1u; }
+    __device__ __forceinline__ void advance(uint32_t step) {   // step <= SIZE
+        idx += step;
+        if (idx >= (uint32_t)SIZE) { idx -= SIZE; lap ^= 1u; }
+    }
+};
+
+__device__ __forceinline__ uint32_t lds_u32(uint32_t smem_addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr));
+    return v;
 }
 
 // ------------------------------------------------------------------ proxies / fences
@@ -83,21 +106,29 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
 
 // ------------------------------------------------------------------ bulk copies (TMA)
 // 1-D bulk copy global -> shared.  dst/src 16-byte aligned, bytes a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
+__device__ __forceinline__ void bulk_g2s(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar,
                                          uint64_t policy) {
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-        ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar), "l"(policy)
         : "memory");
 }
 // 2-D tiled tensor copy global -> shared through a tensor map.  x is the innermost coordinate.
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
-                                            uint64_t* bar, uint64_t policy) {
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
+                                            uint32_t bar, uint64_t policy) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
         " [%0], [%1, {%2, %3}], [%4], %5;"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)),
-        "l"(policy)
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+        : "memory");
+}
+// 3-D variant; x is the innermost coordinate.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
+                                            uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
         : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
@@ -106,9 +137,8 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
 
 // ------------------------------------------------------------------ tensor memory
 // Whole-warp calls.  `ncols` is a power of two >= 32; the base address is written to *smem_holder.
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)),
-                 "r"(ncols)
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_holder, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_holder), "r"(ncols)
                  : "memory");
 }
 __device__ __forceinline__ void tmem_relinquish() {
@@ -124,9 +154,8 @@ __device__ __forceinline__ void tc_fence_after_sync() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 // mbarrier arrives (count 1) when every tcgen05 operation this thread issued so far has completed.
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }

@@ -33,8 +33,9 @@ const char* fp6b200_error_string(int code);
  * The linear layer on device buffers, asynchronous on `stream` (a cudaStream_t).
  * Stands in for fp_eXmY_linear_kernel (fp6_llm/csrc/fp6_linear.cuh:20-32; with e_bits=3, m_bits=2
  * also for fp6_linear_kernel, :8-18).  `workspace` holds split_k*M*N floats and is only touched
- * when split_k > 1.  split_k == 0 lets the library pick (fp6b200_choose_split_k with the SM count of
- * the current device); size the workspace with fp6b200_workspace_bytes(M, N, K, 0) in that case.
+ * when split_k > 1.  split_k == 0 lets the library decompose the work itself (whole waves of output tiles,
+ * then the K blocks of the remaining tiles dealt out evenly over the SMs and summed by a fix-up kernel);
+ * size the workspace with fp6b200_workspace_bytes(M, N, K, 0) in that case.
  * Unsupported shapes/formats return cudaErrorInvalidValue instead of asserting or exiting.
  */
 int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,
@@ -53,9 +54,10 @@ int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev
 size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k);
 
 /*
- * Split-K choice for this kernel on a GPU with `num_sms` SMs (148 on B200); accounts for the 128-row
- * tiles, the CTAs resident per SM and the K blocks available.  The reference's own heuristic
- * (HeuristicFuntion_SplitK, fp6_llm/__init__.py:13-23) is kept separately, unchanged, in Python.
+ * Split count for callers that keep the reference's explicit split-K scheme: the best split_k >= 1 for this
+ * kernel on a GPU with `num_sms` SMs (148 on B200), given its 128-row tiles, one CTA per SM and the K blocks
+ * available.  The reference's own heuristic (HeuristicFuntion_SplitK, fp6_llm/__init__.py:13-23) is kept
+ * separately, unchanged, in Python.  Passing split_k = 0 to fp6b200_linear is usually faster than either.
  */
 int fp6b200_choose_split_k(size_t M, size_t N, size_t K, int num_sms);
 

@@ -81,4 +81,68 @@ void harness_split_range(uint32_t k_blocks, uint32_t splits, uint32_t z, uint32_
 
 uint16_t harness_bias_bits(int e_bits) { return bias_half_bits(e_bits); }
 
+// Walks the work plan of every CTA and checks it against the fix-up arithmetic:
+//  * every unit (tile, K block) is covered exactly once;
+//  * for every remainder tile, summing the slots the fix-up side computes covers exactly its K range.
+// Returns 0 when consistent, else a small error code.
+int harness_check_plan(uint32_t mode, uint32_t m_tiles, uint32_t n_tiles, uint32_t kblocks, uint32_t split_k,
+                       uint32_t grid) {
+    WorkPlan p{mode, m_tiles, n_tiles, kblocks, split_k, grid};
+    const uint32_t tiles = plan_tiles(p);
+    std::vector<uint32_t> cover((size_t)tiles * kblocks, 0);
+    std::vector<int64_t> slot_tile((size_t)2 * grid, -1);
+    std::vector<uint32_t> slot_kb((size_t)2 * grid, 0);
+    std::vector<uint32_t> direct(tiles, 0), split_seen((size_t)tiles * (split_k ? split_k : 1), 0);
+    for (uint32_t c = 0; c < grid; c++) {
+        SegmentIter it;
+        plan_start(p, c, &it);
+        Segment s;
+        uint32_t count = 0;
+        while (plan_next(p, c, &it, &s)) {
+            if (s.nkb == 0 || s.tile >= tiles || s.kb_begin + s.nkb > kblocks) return 1;
+            for (uint32_t k = 0; k < s.nkb; k++) cover[(size_t)s.tile * kblocks + s.kb_begin + k]++;
+            if (s.out_kind == kOutDirect) {
+                if (s.nkb != kblocks) return 2;
+                direct[s.tile]++;
+            } else if (s.out_kind == kOutSlotPartial) {
+                if (mode != kStreamK || s.out_index >= 2 * grid || slot_tile[s.out_index] != -1) return 3;
+                slot_tile[s.out_index] = s.tile;
+                slot_kb[s.out_index] = s.nkb;
+            } else {
+                if (mode != kClassic || s.out_index >= split_k) return 4;
+                split_seen[(size_t)s.tile * split_k + s.out_index]++;
+            }
+            if (++count > tiles * (split_k ? split_k : 1) + 4) return 5;
+        }
+    }
+    for (uint32_t v : cover) if (v != 1) return 6;
+    if (mode == kClassic) {
+        if (split_k > 1) for (uint32_t v : split_seen) if (v != 1) return 7;
+        return 0;
+    }
+    const uint32_t waves = plan_full_waves(p), rem = plan_rem_tiles(p);
+    for (uint32_t r = 0; r < rem; r++) {
+        const uint32_t tile = waves * grid + r;
+        uint32_t first, last;
+        plan_tile_owners(p, r, &first, &last);
+        if (first > last || last >= grid) return 8;
+        if (first == last) {
+            if (direct[tile] != 1) return 9;
+            continue;
+        }
+        if (direct[tile] != 0) return 10;
+        uint32_t sum = 0;
+        for (uint32_t c = first; c <= last; c++) {
+            if (plan_rem_begin(p, c) == plan_rem_begin(p, c + 1)) continue;   // this CTA got no units
+            const uint32_t slot = plan_tile_slot(p, r, c);
+            if (slot_tile[slot] != (int64_t)tile) return 11;
+            sum += slot_kb[slot];
+            slot_tile[slot] = -2;   // consumed
+        }
+        if (sum != kblocks) return 12;
+    }
+    for (int64_t t : slot_tile) if (t >= 0) return 13;   // a partial nobody sums
+    return 0;
+}
+
 }  // extern "C"
