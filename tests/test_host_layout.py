@@ -59,3 +59,18 @@ def test_split_ranges_cover_k(harness):
                 assert b.value == nxt
                 nxt += c.value
             assert nxt == kb
+
+
+def test_work_plans_cover_every_unit_once(harness):
+    """Classic split-K and the wave + stream-K plan: every (tile, K block) is covered exactly once, and the slots
+    the fix-up kernel sums are exactly the partial segments the GEMM CTAs write."""
+    import itertools
+    n = 0
+    for mode in (0, 1):
+        for mt, nt, kb, grid in itertools.product((1, 2, 3, 32, 86, 96, 172, 448), (1, 2, 9), (1, 2, 7, 64, 172), (1, 2, 3, 147, 148)):
+            for sk in ((1, 2, 3, 5, kb) if mode == 0 else (1,)):
+                if sk > kb:
+                    continue
+                assert harness.harness_check_plan(mode, mt, nt, kb, sk, grid) == 0, (mode, mt, nt, kb, sk, grid)
+                n += 1
+    assert n > 1000
