@@ -10,8 +10,8 @@
 //               swizzle, rows past N zero-filled), then the packed weight segments with 1-D bulk copies
 //               (the packed layout keeps all of K contiguous per 64-row block and segment, so no tensor
 //               map is needed and one copy per segment and row block covers the whole stage);
-//   warps 6-21  unpack the segments with shift/LOP3/PRMT sequences, apply 2^bias * scale[row] in fp16
-//               and write the fp16 weights STRAIGHT INTO TENSOR MEMORY with tcgen05.st.16x128b: the
+//   warps 6-21  unpack the segments with shift/LOP3/PRMT sequences into fp16 bit patterns (code value / 2^bias,
+//               exact) and write them STRAIGHT INTO TENSOR MEMORY with tcgen05.st.16x128b: the
 //               reference's packed format hands every lane exactly the registers of an m16k16 A
 //               fragment, which is the register pattern of that store, so the dequantised weights
 //               never touch shared memory;
@@ -19,7 +19,9 @@
 //               fp32 in tensor memory; narrow tiles are issued by up to four warps, each into its own
 //               accumulator, because one thread cannot issue MMAs fast enough for them.  At the end of a
 //               segment the same four warps (one per tensor-memory lane quadrant) read the accumulators
-//               with tcgen05.ld, add them and store fp16 output or fp32 partials.
+//               with tcgen05.ld, add them, multiply by 2^bias * scale[row] in fp32 (the per-row scale is
+//               applied here, once per output, not once per weight: the unpack warps are the bottleneck at
+//               small batch) and store fp16 output or fp32 partials.
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records a code in a status word, drains its
 // own copies, frees its tensor memory and returns.
@@ -35,6 +37,12 @@
 namespace fpx {
 
 namespace {
+
+#ifndef FPX_KS_SMALL
+#define FPX_KS_SMALL 2
+#endif
+// K blocks (64 wide) per pipeline stage for a given tile width
+constexpr int gemm_ks(int n_tile) { return n_tile <= 32 ? FPX_KS_SMALL : (n_tile <= 128 ? 2 : 1); }
 
 constexpr int kTileM = 128;
 constexpr int kAColsPerKBlock = 32;      // 64 fp16 along K per tensor-memory lane
@@ -71,14 +79,14 @@ struct RawBlock {
 template <int BW, int N_TILE>
 struct Config {
     using Raw = RawBlock<BW>;
-    static constexpr int ks = N_TILE <= 128 ? 2 : 1;
-    static constexpr int stages = N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 7 : 5));
-    static constexpr int a_stages = N_TILE <= 64 ? 6 : (N_TILE <= 128 ? 4 : 5);
+    static constexpr int ks = gemm_ks(N_TILE);
+    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : 5) : (N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 7 : 5)));
+    static constexpr int a_stages = ks == 4 ? 3 : (N_TILE <= 64 ? 6 : (N_TILE <= 128 ? 4 : 5));
     // when the A ring is as deep as the shared-memory ring one commit frees a whole stage
     static constexpr bool unified = a_stages == stages;
     // One thread can issue an MMA only every ~60-90 cycles, far more than a narrow MMA needs on the tensor
     // pipe, so narrow tiles are issued by several warps, each into its own accumulator (summed in the epilogue).
-    static constexpr int issuers = N_TILE <= 32 ? 4 : (N_TILE <= 128 ? 2 : 1);
+    static constexpr int issuers = N_TILE <= 32 ? (ks == 4 ? 2 : 4) : (N_TILE <= 128 ? 2 : 1);
     static constexpr int acc_bufs = 1;   // the issuing warps also run the epilogue, so one set of accumulators suffices
     static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
     static constexpr uint32_t w_off = ks * b_block;
@@ -90,10 +98,14 @@ struct Config {
     static constexpr uint32_t acc_col0 = a_stages * a_cols;
     static constexpr uint32_t acc_stride = N_TILE < 32 ? 32u : (uint32_t)N_TILE;
     static constexpr int readers = 4 * ks;   // unpack warps per stage
+    // An issuer waits on a ring slot only every `issuers` stages.  A parity wait is only meaningful when the
+    // slot's previous phase is already complete, which the issuer knows from its own previous wait as long as
+    // the rings are at least `issuers` deep.
+    static_assert(a_stages >= issuers && stages >= issuers, "rings must be at least as deep as the number of issuers");
     static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
     static_assert(acc_col0 + acc_bufs * issuers * acc_stride <= kTmemCols, "tensor memory budget");
     static constexpr int num_barriers = 3 * stages + 2 * a_stages + 2 * acc_bufs;
-    static constexpr uint32_t smem_bytes = stages * stage_bytes + num_barriers * 8u + 16u;
+    static constexpr uint32_t smem_bytes = stages * stage_bytes + num_barriers * 8u + 32u;
     static_assert(2u * smem_bytes > 228u * 1024u, "two CTAs must never share an SM: each takes all of tensor memory");
     static_assert(smem_bytes <= 227u * 1024u, "shared memory budget");
 };
@@ -117,6 +129,8 @@ __device__ unsigned long long g_prof[160][kWarps][8];
 #define PROF_FLUSH() do { } while (0)
 #endif
 
+constexpr uint32_t kMaxGrid = 256;   // CTAs the fix-up kernel's slot list can hold
+
 struct Params {
     const uint8_t* weight;
     const __half* scales;
@@ -126,12 +140,6 @@ struct Params {
     WorkPlan plan;
     int* status;
 };
-
-__device__ __forceinline__ uint32_t scale_pair(uint32_t pat, __half2 c) {
-    __half2 v = *reinterpret_cast<__half2*>(&pat);
-    v = __hmul2(v, c);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 template <int BW, int N_TILE>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -166,6 +174,9 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
     const uint32_t cta = blockIdx.x;
     const WorkPlan plan = p.plan;
 
+    // The reduction / fix-up kernel that may follow is launched with programmatic stream serialisation: let it
+    // become resident now; it waits for this grid to finish before it reads anything.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if ((ring & 1023u) != 0u) {   // uniform over the CTA: nothing has been set up yet
         if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrSmemAlign);
         return;
@@ -325,45 +336,46 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
             const uint32_t m_tile = seg.tile / plan.n_tiles, n_tile = seg.tile % plan.n_tiles;
             const uint32_t row_in_tile = 32u * q + lane;
             const uint32_t row = m_tile * kTileM + row_in_tile;
-#ifdef FPX_EPI_SCALE
+            // the accumulator holds sum(x * pattern); pattern = code value / 2^bias, so scale by 2^bias * scale[row] here, in fp32
             const float row_scale = __half2float(p.scales[row]) * (float)(1u << (16 - (1 << (E_BITS - 1))));
-#else
-            const float row_scale = 1.0f;
-#endif
             if (!PROF_WAIT(5, ptx::mbar_wait(acc_full, nseg & 1u, abort_word, kErrAccFull, 64))) { ok = false; break; }
             ptx::tc_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::acc_col0;
             const uint32_t parts = nstages < (uint32_t)NI ? nstages : (uint32_t)NI;   // issuers that contributed
+            constexpr int CH = 16;   // columns handled per round
 #pragma unroll 1
-            for (int c0 = 0; c0 < N_TILE; c0 += 8) {
+            for (int c0 = 0; c0 < N_TILE; c0 += CH) {
                 const uint32_t n0 = n_tile * N_TILE + c0;
                 if (n0 >= p.N) break;
-                uint32_t v[8];
-                ptx::tmem_ld_32x32b_x8(acc + c0, v);
+                uint32_t v[CH];
+                float f[CH];
+                ptx::tmem_ld_cols<CH>(acc + c0, v);
                 ptx::tc_wait_ld();
-                float f[8];
 #pragma unroll
-                for (int u = 0; u < 8; u++) f[u] = __uint_as_float(v[u]);
+                for (int u = 0; u < CH; u++) f[u] = __uint_as_float(v[u]);
 #pragma unroll
                 for (uint32_t i = 1; i < (uint32_t)NI; i++)
                     if (i < parts) {
-                        ptx::tmem_ld_32x32b_x8(acc + i * Cfg::acc_stride + c0, v);
+                        ptx::tmem_ld_cols<CH>(acc + i * Cfg::acc_stride + c0, v);
                         ptx::tc_wait_ld();
 #pragma unroll
-                        for (int u = 0; u < 8; u++) f[u] += __uint_as_float(v[u]);
+                        for (int u = 0; u < CH; u++) f[u] += __uint_as_float(v[u]);
                     }
+                if (seg.out_kind == kOutDirect) {
+                    __half* dst = p.out + (size_t)n0 * p.M + row;
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    const uint32_t n = n0 + u;
-                    if (n < p.N) {
-                        const float val = f[u] * row_scale;
-                        if (seg.out_kind == kOutDirect)
-                            p.out[(size_t)n * p.M + row] = __float2half_rn(val);
-                        else if (seg.out_kind == kOutSplitPartial)
-                            p.workspace[((size_t)seg.out_index * p.N + n) * p.M + row] = val;
-                        else
-                            p.workspace[((size_t)seg.out_index * N_TILE + (c0 + u)) * kTileM + row_in_tile] = val;
-                    }
+                    for (int u = 0; u < CH; u++)
+                        if (n0 + u < p.N) dst[(size_t)u * p.M] = __float2half_rn(f[u] * row_scale);
+                } else if (seg.out_kind == kOutSplitPartial) {
+                    float* dst = p.workspace + ((size_t)seg.out_index * p.N + n0) * p.M + row;
+#pragma unroll
+                    for (int u = 0; u < CH; u++)
+                        if (n0 + u < p.N) dst[(size_t)u * p.M] = f[u] * row_scale;
+                } else {
+                    float* dst = p.workspace + ((size_t)seg.out_index * N_TILE + c0) * kTileM + row_in_tile;
+#pragma unroll
+                    for (int u = 0; u < CH; u++)
+                        if (n0 + u < p.N) dst[u * kTileM] = f[u] * row_scale;
                 }
             }
             ptx::tc_fence_before_sync();
@@ -381,7 +393,6 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
         const uint32_t turn = group / KS;                        // it takes the stages j with j % kStageGroups == turn
         const int h = q & 1;                                      // sub-blocks 2h, 2h+1 of the 64-row block
         const int rb = q >> 1;                                    // 64-row block inside the 128-row tile
-        const int g = lane >> 2;
         const uint32_t lane_base = ring + 4u * lane;
         const uint32_t o4 = Cfg::off4 + (rb * KS + kbi) * Raw::seg4 + 2 * h * 128;
         const uint32_t o2 = Cfg::off2 + (rb * KS + kbi) * Raw::seg2 + h * 128;
@@ -394,32 +405,6 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
         PROF_DECL
         plan_start(plan, cta, &iter);
         while (ok && plan_next(plan, cta, &iter, &seg)) {
-#ifndef FPX_EPI_SCALE
-            // per-row constant 2^bias * scale (exact in fp16 unless it overflows; then multiply in two steps,
-            // like the reference's MultScale, utils_parallel_dequant.cuh:30-42)
-            const __half bias_h = __ushort_as_half(bias_half_bits(E_BITS));
-            const __half2 bias2 = __half2half2(bias_h);
-            const uint32_t row0 = (seg.tile / plan.n_tiles) * kTileM + 32u * q;
-            __half2 c2[2][2];
-            bool overflow = false;
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++) {
-                    const __half s = p.scales[row0 + 16 * kk + 8 * hr + g];
-                    const __half c = __hmul(s, bias_h);
-                    overflow |= __hisinf(c) || __hisnan(c);
-                    c2[kk][hr] = __halves2half2(c, s);    // low: folded constant, high: plain scale
-                }
-            const bool two_step = __any_sync(0xffffffffu, overflow);
-#pragma unroll
-            for (int kk = 0; kk < 2; kk++)
-#pragma unroll
-                for (int hr = 0; hr < 2; hr++)
-                    c2[kk][hr] = two_step ? __half2half2(__high2half(c2[kk][hr])) : __half2half2(__low2half(c2[kk][hr]));
-#else
-            (void)g;
-#endif
             const uint32_t nstages = (seg.nkb + KS - 1) / KS;
             // this warp's first stage of the segment
             uint32_t t = (turn + kStageGroups - (j0 % kStageGroups)) % kStageGroups;
@@ -468,13 +453,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
                         for (int kk = 0; kk < 2; kk++)
 #pragma unroll
                             for (int i = 0; i < 4; i++) {
-#ifndef FPX_EPI_SCALE
-                                uint32_t x = pat[4 * kk + i];
-                                if (two_step) x = scale_pair(x, bias2);
-                                v[kk][4 * jj + i] = scale_pair(x, c2[kk][i & 1]);   // a0,a2: row g; a1,a3: row g+8
-#else
                                 v[kk][4 * jj + i] = pat[4 * kk + i];
-#endif
                             }
                     }
 #endif
@@ -528,6 +507,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__ out, const float* __restrict__ partials,
                                                             size_t elems, int split_k) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialisation
     if (i >= elems) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < split_k; s++) {
@@ -544,10 +524,12 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
 // Fix-up of the stream-K remainder: CTA = (remainder tile, token column), thread = output channel.  Sums, in CTA
 // order, the partial slots of every CTA that worked on the tile (fp32) and stores fp16; tiles that one CTA
 // computed alone were stored directly and are skipped.  Four running sums keep several loads in flight.
+// (Summing inside the GEMM by the CTA that delivers a tile's last part was measured slower: its dependent global
+// round trips cost more than this launch, and wide tiles are then summed by one SM instead of all.)
 __global__ void __launch_bounds__(kTileM) streamk_fixup_kernel(__half* __restrict__ out, const float* __restrict__ slots,
                                                                uint32_t M, uint32_t N, int n_tile_size, WorkPlan plan) {
-    __shared__ uint32_t cand_slot[2 * kTileM];   // per candidate CTA: its slot, or ~0u when it holds nothing
-    __shared__ uint32_t part_slot[2 * kTileM];   // slots that hold a part of this tile, in CTA order
+    __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
+    __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
     const uint32_t r = blockIdx.x, c = blockIdx.y;
     uint32_t first, last;
@@ -557,7 +539,7 @@ __global__ void __launch_bounds__(kTileM) streamk_fixup_kernel(__half* __restric
     const uint32_t m_tile = tile / plan.n_tiles, n_tile = tile % plan.n_tiles;
     const uint32_t n = n_tile * n_tile_size + c;
     if (n >= N) return;
-    const uint32_t span = last - first + 1 < 2u * kTileM ? last - first + 1 : 2u * kTileM;
+    const uint32_t span = last - first + 1 < kMaxGrid ? last - first + 1 : kMaxGrid;
     for (uint32_t i = threadIdx.x; i < span; i += kTileM) {   // one candidate CTA per thread
         const uint32_t cta = first + i;
         const bool holds = plan_rem_begin(plan, cta) != plan_rem_begin(plan, cta + 1);
@@ -573,6 +555,7 @@ __global__ void __launch_bounds__(kTileM) streamk_fixup_kernel(__half* __restric
     __syncthreads();
     const uint32_t row = threadIdx.x;
     const uint32_t count = part_count;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the GEMM grid has completed and its stores are visible
     const float* base = slots + (size_t)c * kTileM + row;
     const size_t slot_stride = (size_t)n_tile_size * kTileM;
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
@@ -672,13 +655,23 @@ int gemm_n_tile(size_t N) { return N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 
 
 size_t gemm_auto_workspace_bytes(size_t N) {
     // stream-K: two partial slots of 128 x n_tile fp32 per CTA
-    return (size_t)2 * device_sm_count() * kTileM * gemm_n_tile(N) * sizeof(float);
+    const size_t ctas = device_sm_count() < (int)kMaxGrid ? device_sm_count() : kMaxGrid;
+    return 2 * ctas * kTileM * gemm_n_tile(N) * sizeof(float);
 }
 
-cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k) {
+cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k,
+                                 bool after_gemm) {
     const size_t threads = (elems + 3) / 4;
-    splitk_reduce_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(out, partials, elems, split_k);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = after_gemm ? 1 : 0;   // overlap the launch with the GEMM's tail
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, out, partials, elems, split_k);
 }
 
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
@@ -696,10 +689,10 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     const size_t n_tiles = (N + n_tile - 1) / n_tile;
     if ((M / kTileM) * n_tiles > 0x3fffffffull) return cudaErrorInvalidValue;
     CUtensorMap map;
-    cudaError_t err = make_act_map(&map, act, N, K, n_tile, n_tile <= 128 ? 2 : 1);
+    cudaError_t err = make_act_map(&map, act, N, K, n_tile, gemm_ks(n_tile));
     if (err != cudaSuccess) return err;
 
-    const int sms = device_sm_count();
+    const int sms = device_sm_count() < (int)kMaxGrid ? device_sm_count() : (int)kMaxGrid;
     Params prm;
     prm.weight = static_cast<const uint8_t*>(weight);
     prm.scales = scales;
@@ -727,16 +720,25 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         const uint64_t items = tiles * eff_split;
         plan.grid = (uint32_t)(items < (uint64_t)sms ? items : (uint64_t)sms);
     }
+    plan_finalize(&plan);
     const int bw = 1 + e_bits + m_bits;
     err = bw == 6 ? launch_by_n<6>(n_tile, stream, map, prm) : launch_by_n<5>(n_tile, stream, map, prm);
     if (err != cudaSuccess) return err;
     if (plan.mode == kStreamK) {
         const uint32_t rem = plan_rem_tiles(plan);
         if (rem == 0) return cudaSuccess;
-        streamk_fixup_kernel<<<dim3(rem, (unsigned)n_tile), kTileM, 0, stream>>>(out, workspace, (uint32_t)M, (uint32_t)N, n_tile, plan);
-        return cudaGetLastError();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(rem, (unsigned)n_tile);
+        cfg.blockDim = dim3(kTileM);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, out, (const float*)workspace, (uint32_t)M, (uint32_t)N, n_tile, plan);
     }
-    if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split);
+    if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true);
     return cudaSuccess;
 }
 

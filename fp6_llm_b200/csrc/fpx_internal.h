@@ -14,7 +14,8 @@ inline bool format_supported(int e_bits, int m_bits) { return m_bits == 2 && (e_
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
                         int* status);
-cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k);
+cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k,
+                                 bool after_gemm = false);
 int gemm_n_tile(size_t N);
 int device_sm_count();
 // Workspace the GEMM needs when it picks its own decomposition (split_k == 0).

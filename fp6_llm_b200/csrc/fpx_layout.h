@@ -184,6 +184,10 @@ struct WorkPlan {
     uint32_t kblocks;     // K / 64
     uint32_t split_k;     // kClassic only (1 <= split_k <= kblocks)
     uint32_t grid;        // number of CTAs
+    // derived by plan_finalize (so that device code does not redo the divisions)
+    uint32_t full_waves;  // tiles / grid
+    uint32_t rem_tiles;   // tiles - full_waves * grid
+    uint32_t rem_units32; // rem_tiles * kblocks when (rem_tiles * kblocks + 1) * grid fits 32 bits, else 0
 };
 
 struct Segment {
@@ -195,15 +199,23 @@ struct Segment {
 };
 
 FPX_HD uint32_t plan_tiles(const WorkPlan& p) { return p.m_tiles * p.n_tiles; }
-FPX_HD uint32_t plan_full_waves(const WorkPlan& p) { return plan_tiles(p) / p.grid; }
-FPX_HD uint32_t plan_rem_tiles(const WorkPlan& p) { return plan_tiles(p) - plan_full_waves(p) * p.grid; }
+FPX_HD void plan_finalize(WorkPlan* p) {
+    p->full_waves = plan_tiles(*p) / p->grid;
+    p->rem_tiles = plan_tiles(*p) - p->full_waves * p->grid;
+    const uint64_t units = (uint64_t)p->rem_tiles * p->kblocks;
+    p->rem_units32 = (units + 1) * p->grid <= 0xffffffffull ? (uint32_t)units : 0u;
+}
+FPX_HD uint32_t plan_full_waves(const WorkPlan& p) { return p.full_waves; }
+FPX_HD uint32_t plan_rem_tiles(const WorkPlan& p) { return p.rem_tiles; }
 // first remainder unit of CTA c (kStreamK); c == grid gives the total
 FPX_HD uint64_t plan_rem_begin(const WorkPlan& p, uint32_t c) {
-    return (uint64_t)c * ((uint64_t)plan_rem_tiles(p) * p.kblocks) / p.grid;
+    if (p.rem_units32) return (uint64_t)(c * p.rem_units32 / p.grid);
+    return (uint64_t)c * ((uint64_t)p.rem_tiles * p.kblocks) / p.grid;
 }
 // CTA that owns remainder unit u
 FPX_HD uint32_t plan_rem_owner(const WorkPlan& p, uint64_t u) {
-    const uint64_t total = (uint64_t)plan_rem_tiles(p) * p.kblocks;
+    if (p.rem_units32) return ((uint32_t)(u + 1) * p.grid - 1u) / p.rem_units32;
+    const uint64_t total = (uint64_t)p.rem_tiles * p.kblocks;
     return (uint32_t)(((u + 1) * p.grid - 1) / total);
 }
 

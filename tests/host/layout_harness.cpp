@@ -87,7 +87,8 @@ uint16_t harness_bias_bits(int e_bits) { return bias_half_bits(e_bits); }
 // Returns 0 when consistent, else a small error code.
 int harness_check_plan(uint32_t mode, uint32_t m_tiles, uint32_t n_tiles, uint32_t kblocks, uint32_t split_k,
                        uint32_t grid) {
-    WorkPlan p{mode, m_tiles, n_tiles, kblocks, split_k, grid};
+    WorkPlan p{mode, m_tiles, n_tiles, kblocks, split_k, grid, 0, 0, 0};
+    plan_finalize(&p);
     const uint32_t tiles = plan_tiles(p);
     std::vector<uint32_t> cover((size_t)tiles * kblocks, 0);
     std::vector<int64_t> slot_tile((size_t)2 * grid, -1);
