@@ -15,10 +15,10 @@ _ROOT = os.path.dirname(_PKG)
 _CSRC = os.path.join(_PKG, "csrc")
 LIB_DIR = os.path.join(_PKG, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libfp6_b200.so")
-SOURCES = ("fpx_gemm.cu", "fpx_prepack.cu", "c_api.cu")
+SOURCES = ("fpx_gemm.cu", "fpx_prepack.cu", "c_api.cu", "c_api_noalloc.cu")
 HEADERS = ("fpx_internal.h", "fpx_layout.h", "ptx_sm100.cuh")
 
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--threads", "4",
               "-Xcompiler", "-fPIC", "-shared"]
 
 # every symbol include/fp6_llm_b200.h declares
@@ -26,7 +26,7 @@ C_SYMBOLS = (
     "fp6b200_version", "fp6b200_error_string", "fp6b200_linear", "fp6b200_linear_host_io",
     "fp6b200_workspace_bytes", "fp6b200_choose_split_k", "fp6b200_prepack", "fp6b200_prepack_host",
     "fp6b200_dequant", "fp6b200_dequant_host", "fp6b200_dequant_packed", "fp6b200_splitk_reduce",
-    "fp6b200_device_status",
+    "fp6b200_device_status", "fp6b200_linear_static_scratch", "fp6b200_static_scratch_bytes",
 )
 
 
@@ -99,6 +99,10 @@ def lib() -> ctypes.CDLL:
     L.fp6b200_dequant_packed.argtypes = [ci, ci, vp, vp, vp, vp, sz, sz]
     L.fp6b200_splitk_reduce.restype = ci
     L.fp6b200_splitk_reduce.argtypes = [vp, vp, vp, sz, ci]
+    L.fp6b200_linear_static_scratch.restype = ci
+    L.fp6b200_linear_static_scratch.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz]
+    L.fp6b200_static_scratch_bytes.restype = sz
+    L.fp6b200_static_scratch_bytes.argtypes = []
     L.fp6b200_device_status.restype = ci
     L.fp6b200_device_status.argtypes = [ctypes.POINTER(ci)]
     _lib = L

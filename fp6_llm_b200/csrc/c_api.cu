@@ -94,6 +94,10 @@ int choose_split_k(size_t M, size_t N, size_t K, int num_sms) {
 
 }  // namespace
 
+namespace fpx {
+int* gemm_status_word() { return status_ptr(); }
+}  // namespace fpx
+
 extern "C" {
 
 int fp6b200_version(void) { return 1; }

@@ -21,6 +21,9 @@ int device_sm_count();
 // Workspace the GEMM needs when it picks its own decomposition (split_k == 0).
 size_t gemm_auto_workspace_bytes(size_t N);
 
+// Device address (current device) of the word in which a GEMM CTA records a time-out; nullptr on failure.
+int* gemm_status_word();
+
 // Weight format kernels.  All pointers are device pointers; in != out.
 cudaError_t launch_prepack(int e_bits, int m_bits, cudaStream_t stream, const void* unpacked, void* packed, size_t M,
                            size_t K);

@@ -101,6 +101,22 @@ int fp6b200_dequant_packed(int e_bits, int m_bits, void* stream, const void* pac
 int fp6b200_splitk_reduce(void* stream, void* out_dev, const float* partials_dev, size_t elems, int split_k);
 
 /*
+ * The linear layer for callers that cannot allocate and cannot pass a workspace (no counterpart in the reference,
+ * whose torch wrapper allocates a workspace on every call).  Same arguments and result as fp6b200_linear with
+ * split_k = 0, but the fp32 scratch is a fixed array of fp6b200_static_scratch_bytes() bytes inside the library:
+ * every GPU that loads the library holds it until the process exits.  Returns cudaErrorInvalidValue (and says why on
+ * stderr) when fp6b200_workspace_bytes(M, N, K, 0) exceeds that size (batch sizes above 64 on a 148-SM GPU).
+ * Makes no cudaMalloc/cudaFree or other allocating call.  The first call on a device looks the array's address up
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device share the array:
+ * calls whose kernels can overlap on the GPU race; order them on one stream.
+ */
+int fp6b200_linear_static_scratch(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,
+                                  const void* act, void* out, size_t M, size_t N, size_t K);
+
+/* Size in bytes of the built-in scratch array used by fp6b200_linear_static_scratch. */
+size_t fp6b200_static_scratch_bytes(void);
+
+/*
  * Synchronises the current device, returns in *code the first time-out code a GEMM CTA recorded
  * since the last call (0 = none) and clears it.  A non-zero code means a bounded wait inside the
  * kernel gave up and the output of that launch is invalid.
