@@ -39,7 +39,7 @@ namespace fpx {
 namespace {
 
 #ifndef FPX_KS_SMALL
-#define FPX_KS_SMALL 2
+#define FPX_KS_SMALL 4
 #endif
 // K blocks (64 wide) per pipeline stage for a given tile width
 constexpr int gemm_ks(int n_tile) { return n_tile <= 32 ? FPX_KS_SMALL : (n_tile <= 128 ? 2 : 1); }
