@@ -181,22 +181,30 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
         if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrSmemAlign);
         return;
     }
-    if (warp == 1) {   // barrier set-up, one barrier per lane and round
+    // Set-up.  The first producer warp initialises every barrier; the two producer warps then meet on a barrier of
+    // their own and start copying at once, while the rest of the CTA waits for the tensor-memory allocation too.
+    if (warp == kProducerWarp) {   // one barrier per lane and round
         for (int i = lane; i < R; i += 32) { ptx::mbar_init(full + 8 * i, kProducerWarps); ptx::mbar_init(w_empty + 8 * i, Cfg::readers); ptx::mbar_init(b_empty + 8 * i, 1); }
         for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, 1); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
         if (lane == 0) *abort_word = 0;
         ptx::fence_barrier_init();
+        if (lane == 0) ptx::prefetch_tensormap(&act_map);
     }
     if (warp == 0) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTmemCols);
         ptx::tmem_relinquish();
     }
-    if (warp == kProducerWarp && lane == 0) ptx::prefetch_tensormap(&act_map);
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_holder;
+    if (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) {
+        __threadfence_block();
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kProducerWarps) : "memory");   // producers: the barriers exist
+        asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");            // tell the others, do not wait
+    } else {
+        ptx::tc_fence_before_sync();
+        asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
+        ptx::tc_fence_after_sync();
+    }
+    const uint32_t tmem_base = *tmem_holder;   // valid for every warp but the producers, which never use it
 
     if (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) {
         // ------------------------------------------------------------ producers: warp 4 copies the activations and the
@@ -521,26 +529,26 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
     *reinterpret_cast<uint2*>(out + i) = packed;
 }
 
-// Fix-up of the stream-K remainder: CTA = (remainder tile, token column), thread = output channel.  Sums, in CTA
-// order, the partial slots of every CTA that worked on the tile (fp32) and stores fp16; tiles that one CTA
-// computed alone were stored directly and are skipped.  Four running sums keep several loads in flight.
+// Fix-up of the stream-K remainder: CTA = (remainder tile, group of kFixupCols token columns); a thread owns four
+// consecutive output channels of one token column (32 threads per column).  Sums, in CTA order, the partial slots of every
+// CTA that worked on the tile (fp32, float4 loads) and stores fp16; tiles that one CTA computed alone were stored
+// directly and are skipped.
 // (Summing inside the GEMM by the CTA that delivers a tile's last part was measured slower: its dependent global
 // round trips cost more than this launch, and wide tiles are then summed by one SM instead of all.)
-__global__ void __launch_bounds__(kTileM) streamk_fixup_kernel(__half* __restrict__ out, const float* __restrict__ slots,
-                                                               uint32_t M, uint32_t N, int n_tile_size, WorkPlan plan) {
+constexpr int kFixupCols = 16;
+__global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(__half* __restrict__ out, const float* __restrict__ slots,
+                                                                         uint32_t M, uint32_t N, int n_tile_size, WorkPlan plan) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
-    const uint32_t r = blockIdx.x, c = blockIdx.y;
+    const uint32_t r = blockIdx.x;
     uint32_t first, last;
     plan_tile_owners(plan, r, &first, &last);
     if (first == last) return;
     const uint32_t tile = plan_full_waves(plan) * plan.grid + r;
     const uint32_t m_tile = tile / plan.n_tiles, n_tile = tile % plan.n_tiles;
-    const uint32_t n = n_tile * n_tile_size + c;
-    if (n >= N) return;
     const uint32_t span = last - first + 1 < kMaxGrid ? last - first + 1 : kMaxGrid;
-    for (uint32_t i = threadIdx.x; i < span; i += kTileM) {   // one candidate CTA per thread
+    for (uint32_t i = threadIdx.x; i < span; i += blockDim.x) {   // one candidate CTA per thread
         const uint32_t cta = first + i;
         const bool holds = plan_rem_begin(plan, cta) != plan_rem_begin(plan, cta + 1);
         cand_slot[i] = holds ? plan_tile_slot(plan, r, cta) : ~0u;
@@ -553,21 +561,26 @@ __global__ void __launch_bounds__(kTileM) streamk_fixup_kernel(__half* __restric
         part_count = cnt;
     }
     __syncthreads();
-    const uint32_t row = threadIdx.x;
     const uint32_t count = part_count;
-    asm volatile("griddepcontrol.wait;" ::: "memory");   // the GEMM grid has completed and its stores are visible
-    const float* base = slots + (size_t)c * kTileM + row;
+    const uint32_t row4 = (threadIdx.x & 31u) * 4u;          // first of this thread's four output channels
     const size_t slot_stride = (size_t)n_tile_size * kTileM;
-    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-    uint32_t i = 0;
-    for (; i + 4 <= count; i += 4) {
-        acc0 += base[part_slot[i] * slot_stride];
-        acc1 += base[part_slot[i + 1] * slot_stride];
-        acc2 += base[part_slot[i + 2] * slot_stride];
-        acc3 += base[part_slot[i + 3] * slot_stride];
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // the GEMM grid has completed and its stores are visible
+    const uint32_t c = blockIdx.y * kFixupCols + (threadIdx.x >> 5);
+    const uint32_t n = n_tile * n_tile_size + c;
+    if (c < (uint32_t)n_tile_size && n < N) {
+        const float* base = slots + (size_t)c * kTileM + row4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (uint32_t i = 0; i < count; i++) {
+            const float4 v = *reinterpret_cast<const float4*>(base + part_slot[i] * slot_stride);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out + (size_t)n * M + m_tile * kTileM + row4) = packed;
     }
-    for (; i < count; i++) acc0 += base[part_slot[i] * slot_stride];
-    out[(size_t)n * M + m_tile * kTileM + row] = __float2half_rn((acc0 + acc1) + (acc2 + acc3));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -728,8 +741,8 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         const uint32_t rem = plan_rem_tiles(plan);
         if (rem == 0) return cudaSuccess;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(rem, (unsigned)n_tile);
-        cfg.blockDim = dim3(kTileM);
+        cfg.gridDim = dim3(rem, (unsigned)((n_tile + kFixupCols - 1) / kFixupCols));
+        cfg.blockDim = dim3(32u * kFixupCols);
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
