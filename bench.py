@@ -157,6 +157,18 @@ def cpu_sample_rows(e, m, layer, batches, n_steps, budget_s):
     return max(64, min(oc, rows))
 
 
+def select_cases(args):
+    """The workload's (e, m, layers, batches); --case LAYER:BATCH narrows it to one launch shape (small profiler runs)."""
+    e, m, layers, batches = WORKLOADS[args.workload]
+    if args.case:
+        name, bs = args.case.split(":")
+        layers = [l for l in layers if l[0] == name]
+        if not layers:
+            raise SystemExit(f"--case: workload {args.workload} has no layer {name!r}")
+        batches = [int(bs)]
+    return e, m, layers, batches
+
+
 def run_reference(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -180,7 +192,7 @@ def run_reference(args):
         "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": secs / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "format": f"e{e}m{m}", "layers": [list(l) for l in layers], "batch_sizes": batches,
+        "config": {"workload": args.workload + (f" [{args.case} only]" if args.case else ""), "format": f"e{e}m{m}", "layers": [list(l) for l in layers], "batch_sizes": batches,
                    "path": "weight_dequant_cpu + fp32 matmul on host cores"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -209,7 +221,7 @@ def run_ours(args):
     f.lib()   # raises if the CUDA library is missing: there is no fallback
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
 
-    e, m, layers, batches = WORKLOADS[args.workload]
+    e, m, layers, batches = select_cases(args)
     bw = bit_width(e, m)
     # ---- weights: seeded N(0, 0.02) -> per-row scale -> round-to-nearest codes -> GPU prepack; replicas for cold L2
     shard_bytes = 0
@@ -373,7 +385,7 @@ def run_ours(args):
             "value": flops_step / sec_step / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": sec_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": args.workload, "format": f"e{e}m{m}", "layers": [list(l) for l in layers], "batch_sizes": batches,
+            "config": {"workload": args.workload + (f" [{args.case} only]" if args.case else ""), "format": f"e{e}m{m}", "layers": [list(l) for l in layers], "batch_sizes": batches,
                        "split_k": "0 (library: tile waves + stream-K remainder)" if args.split_k <= 0 else args.split_k,
                        "parallelism": "single GPU" if world == 1 else f"OC-sharded x{world} + all-gather of [BS, OC]",
                        "l2": f"inputs larger than L2: {replicas} replicas of the layer set ({shard_bytes * replicas / 2**20:.0f} MiB) rotated so a buffer is re-read only after >= 512 MiB of other weights",
@@ -399,6 +411,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--split-k", type=int, default=0, help="0 = let the library decompose the work")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, help="LAYER:BATCH - run only this launch shape of the workload (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -2,7 +2,7 @@
 // library allocate one.
 //
 // Who that is: a serving process that reserves all device memory for its own pools at start-up (a cudaMalloc made
-// later simply fails), a callback that runs while a stream is being captured (allocation is forbidden there), or a
+// later simply fails), or a
 // component whose memory budget is fixed by contract and audited.  Such callers still pass inputs and the output
 // buffer; what they cannot provide is the fp32 scratch the kernel uses when it deals the K range of a tile out over
 // several SMs.  Here that scratch is a fixed array inside the library image.

@@ -536,6 +536,10 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
 // (Summing inside the GEMM by the CTA that delivers a tile's last part was measured slower: its dependent global
 // round trips cost more than this launch, and wide tiles are then summed by one SM instead of all.)
 constexpr int kFixupCols = 16;
+#ifndef FPX_EVEN_PCT
+#define FPX_EVEN_PCT 85
+#endif
+constexpr uint64_t kEvenGridMinPercent = FPX_EVEN_PCT;
 __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(__half* __restrict__ out, const float* __restrict__ slots,
                                                                          uint32_t M, uint32_t N, int n_tile_size, WorkPlan plan) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
@@ -726,6 +730,12 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         plan.split_k = 1;
         const uint64_t units = tiles * plan.kblocks;
         plan.grid = (uint32_t)(units < (uint64_t)sms ? units : (uint64_t)sms);
+        // Fewer tiles than SMs: a grid that is a multiple of the tile count gives every tile the same number of
+        // CTAs and no CTA a second tile (one epilogue per CTA); taken when it still fills most of the SMs.
+        if (tiles < (uint64_t)sms && units >= (uint64_t)sms) {
+            const uint64_t even = tiles * ((uint64_t)sms / tiles);
+            if (even * 100 >= (uint64_t)sms * kEvenGridMinPercent) plan.grid = (uint32_t)even;
+        }
     } else {              // the caller's split: splits beyond the number of K blocks would be empty
         plan.mode = kClassic;
         eff_split = split_k < (int)plan.kblocks ? split_k : (int)plan.kblocks;

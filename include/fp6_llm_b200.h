@@ -107,7 +107,7 @@ int fp6b200_splitk_reduce(void* stream, void* out_dev, const float* partials_dev
  * every GPU that loads the library holds it until the process exits.  Returns cudaErrorInvalidValue (and says why on
  * stderr) when fp6b200_workspace_bytes(M, N, K, 0) exceeds that size (batch sizes above 64 on a 148-SM GPU).
  * Makes no cudaMalloc/cudaFree or other allocating call.  The first call on a device looks the array's address up
- * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device share the array:
+ * (cudaGetSymbolAddress).  All calls on a device share the array:
  * calls whose kernels can overlap on the GPU race; order them on one stream.
  */
 int fp6b200_linear_static_scratch(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,

@@ -1,4 +1,4 @@
-"""The entry point for callers that cannot allocate device memory (pre-reserved pools, stream capture, fixed memory
+"""The entry point for callers that cannot allocate device memory (pre-reserved pools, fixed memory
 budgets): it must give the same output as the ordinary entry point, on two calls in a row (the built-in scratch array
 keeps the first call's contents when the second one runs), and refuse problems its fixed scratch cannot hold."""
 import numpy as np
