@@ -114,6 +114,8 @@ struct Config {
 // spends in each of its waits and in total, and leaves them in g_prof[cta][warp][counter].
 #ifdef FPX_PROFILE
 __device__ unsigned long long g_prof[160][kWarps][8];
+__device__ unsigned long long g_stamp[160][16];   // global-timer stamps (ns) of a CTA's milestones
+#define PROF_STAMP(slot) do { if (blockIdx.x < 160) g_stamp[blockIdx.x][slot] = ptx::global_timer_ns(); } while (0)
 #define PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64();
 #define PROF_WAIT(slot, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); prof_acc[slot] += (unsigned long long)(clock64() - t_); return r_; }()
 #define PROF_BEGIN(var) const long long var = clock64();
@@ -121,6 +123,7 @@ __device__ unsigned long long g_prof[160][kWarps][8];
 #define PROF_COUNT(slot) prof_acc[slot]++;
 #define PROF_FLUSH() do { prof_acc[7] = (unsigned long long)(clock64() - prof_t0); if (lane == 0 && blockIdx.x < 160) for (int i_ = 0; i_ < 8; i_++) g_prof[blockIdx.x][warp][i_] = prof_acc[i_]; } while (0)
 #else
+#define PROF_STAMP(slot) do { } while (0)
 #define PROF_DECL
 #define PROF_WAIT(slot, expr) (expr)
 #define PROF_BEGIN(var)
@@ -133,6 +136,7 @@ constexpr uint32_t kMaxGrid = 256;   // CTAs the fix-up kernel's slot list can h
 
 struct Params {
     const uint8_t* weight;
+    const uint8_t* region[3];   // start of the 1-bit, 2-bit and 4-bit regions of the packed weights
     const __half* scales;
     __half* out;
     float* workspace;
@@ -143,7 +147,7 @@ struct Params {
 
 template <int BW, int N_TILE>
 __global__ void __launch_bounds__(kThreads, 1)
-fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
+fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ Params p) {
     constexpr int E_BITS = BW - 3;   // both supported formats have a 2-bit mantissa
     using Cfg = Config<BW, N_TILE>;
     using Raw = typename Cfg::Raw;
@@ -172,11 +176,12 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t cta = blockIdx.x;
-    const WorkPlan plan = p.plan;
+    const WorkPlan& plan = p.plan;   // stays in the parameter space (it carries a table indexed by CTA)
 
     // The reduction / fix-up kernel that may follow is launched with programmatic stream serialisation: let it
     // become resident now; it waits for this grid to finish before it reads anything.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) PROF_STAMP(0);
     if ((ring & 1023u) != 0u) {   // uniform over the CTA: nothing has been set up yet
         if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrSmemAlign);
         return;
@@ -204,6 +209,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
         asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
         ptx::tc_fence_after_sync();
     }
+    if (threadIdx.x == 0) PROF_STAMP(1);
     const uint32_t tmem_base = *tmem_holder;   // valid for every warp but the producers, which never use it
 
     if (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) {
@@ -211,12 +217,13 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
         // weight segments of the tile's first 64-row block, warp 5 those of the second (one thread each)
         if (lane == 0) {
             const uint32_t half = (uint32_t)(warp - kProducerWarp);
+            if (half == 0) PROF_STAMP(13);
             const uint64_t pol_w = ptx::policy_evict_first();
             const uint64_t pol_b = ptx::policy_evict_last();
             const uint64_t kblocks = plan.kblocks;
-            const uint8_t* reg1 = p.weight + region_offset(BW, 1, p.M, p.K);
-            const uint8_t* reg2 = p.weight + region_offset(BW, 2, p.M, p.K);
-            const uint8_t* reg4 = p.weight + region_offset(BW, 4, p.M, p.K);
+            const uint8_t* reg1 = p.region[0];
+            const uint8_t* reg2 = p.region[1];
+            const uint8_t* reg4 = p.region[2];
             ptx::RingPos<R> pos;
             pos.set(0);
             uint32_t issued = 0;
@@ -226,10 +233,12 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
             PROF_DECL
             plan_start(plan, cta, &iter);
             while (ok && plan_next(plan, cta, &iter, &seg)) {
-                const uint64_t blk0 = ((uint64_t)(seg.tile / plan.n_tiles) * 2 + half) * kblocks + seg.kb_begin;   // my row block, first K block
-                const int32_t n0 = (int32_t)((seg.tile % plan.n_tiles) * N_TILE);
+                const uint32_t m_tile = plan.n_tiles == 1 ? seg.tile : seg.tile / plan.n_tiles;
+                const uint64_t blk0 = ((uint64_t)m_tile * 2 + half) * kblocks + seg.kb_begin;   // my row block, first K block
+                const int32_t n0 = (int32_t)((seg.tile - m_tile * plan.n_tiles) * N_TILE);
                 const uint32_t nstages = (seg.nkb + KS - 1) / KS;
                 uint32_t sidx = plan_first_stage(cta, nstages);   // stage of the segment's K range handled next
+                if (half == 0 && issued == 0) PROF_STAMP(14);
                 for (uint32_t i = 0; i < nstages; i++) {
                     const uint32_t kb_off = sidx * KS;
                     const uint32_t cnt = seg.nkb - kb_off < (uint32_t)KS ? seg.nkb - kb_off : (uint32_t)KS;
@@ -242,6 +251,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
                         if (!PROF_WAIT(1, ptx::mbar_wait(b_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
                     }
                     PROF_COUNT(6)
+                    if (half == 0 && issued == 0) PROF_STAMP(15);
                     PROF_BEGIN(t_issue)
                     const uint32_t bar = full + 8 * pos.idx;
                     const uint32_t dst = ring + pos.idx * Cfg::stage_bytes;
@@ -262,6 +272,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
                     if (Raw::seg4) ptx::bulk_g2s(dst + Cfg::off4 + half * KS * Raw::seg4, reg4 + b0 * Raw::seg4, cnt * Raw::seg4, bar, pol_w);
                     PROF_END(3, t_issue)
                     pos.advance(1);
+                    if (half == 0) { if (issued == 0) PROF_STAMP(2); PROF_STAMP(3); }
                     issued++;
                 }
             }
@@ -305,6 +316,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
                     const uint32_t cnt = seg.nkb - sidx * KS < (uint32_t)KS ? seg.nkb - sidx * KS : (uint32_t)KS;
                     sidx += NI;
                     if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull))) { ok = false; break; }
+                    if (me == 0 && nseg == 0 && t == me) PROF_STAMP(5);
                     // the activations of the stage landed before its weights were unpacked; this only makes them visible here
                     if (!PROF_WAIT(1, ptx::mbar_wait(full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
@@ -329,6 +341,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
                     ptx::tc_commit(a_empty + 8 * ap.idx);
                     if (!kUnified) ptx::tc_commit(b_empty + 8 * rp.idx);
                     PROF_END(4, t_commit)
+                    if (me == 0) PROF_STAMP(6);
                     rp.advance(NI);
                     ap.advance(NI);
                 }
@@ -341,12 +354,13 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
             if (!ok) break;
             j0 += nstages;
 
-            const uint32_t m_tile = seg.tile / plan.n_tiles, n_tile = seg.tile % plan.n_tiles;
+            const uint32_t m_tile = plan.n_tiles == 1 ? seg.tile : seg.tile / plan.n_tiles, n_tile = seg.tile - m_tile * plan.n_tiles;
             const uint32_t row_in_tile = 32u * q + lane;
             const uint32_t row = m_tile * kTileM + row_in_tile;
             // the accumulator holds sum(x * pattern); pattern = code value / 2^bias, so scale by 2^bias * scale[row] here, in fp32
             const float row_scale = __half2float(p.scales[row]) * (float)(1u << (16 - (1 << (E_BITS - 1))));
             if (!PROF_WAIT(5, ptx::mbar_wait(acc_full, nseg & 1u, abort_word, kErrAccFull, 64))) { ok = false; break; }
+            if (threadIdx.x == 0) PROF_STAMP(7);
             ptx::tc_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::acc_col0;
             const uint32_t parts = nstages < (uint32_t)NI ? nstages : (uint32_t)NI;   // issuers that contributed
@@ -389,6 +403,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(acc_empty);
+            if (threadIdx.x == 0) PROF_STAMP(8);
             nseg++;
         }
         PROF_FLUSH();
@@ -426,6 +441,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
                 const bool valid = sidx * KS + kbi < seg.nkb;    // the last stage of the K range may hold fewer K blocks
                 sidx += kStageGroups;
                 if (!PROF_WAIT(0, ptx::mbar_wait(full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == turn) PROF_STAMP(4);
                 PROF_COUNT(6)
                 PROF_BEGIN(t_math)
                 uint32_t v[2][16];
@@ -507,6 +523,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const Params p) {
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_word != 0) atomicCAS(p.status, 0, *abort_word);
+    if (threadIdx.x == 0) PROF_STAMP(9);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -541,11 +558,12 @@ constexpr int kFixupCols = 16;
 #endif
 constexpr uint64_t kEvenGridMinPercent = FPX_EVEN_PCT;
 __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(__half* __restrict__ out, const float* __restrict__ slots,
-                                                                         uint32_t M, uint32_t N, int n_tile_size, WorkPlan plan) {
+                                                                         uint32_t M, uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
     const uint32_t r = blockIdx.x;
+    if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(10);
     uint32_t first, last;
     plan_tile_owners(plan, r, &first, &last);
     if (first == last) return;
@@ -569,6 +587,7 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(__half* 
     const uint32_t row4 = (threadIdx.x & 31u) * 4u;          // first of this thread's four output channels
     const size_t slot_stride = (size_t)n_tile_size * kTileM;
     asm volatile("griddepcontrol.wait;" ::: "memory");       // the GEMM grid has completed and its stores are visible
+    if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(11);
     const uint32_t c = blockIdx.y * kFixupCols + (threadIdx.x >> 5);
     const uint32_t n = n_tile * n_tile_size + c;
     if (c < (uint32_t)n_tile_size && n < N) {
@@ -585,6 +604,7 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(__half* 
         packed.y = *reinterpret_cast<uint32_t*>(&hi);
         *reinterpret_cast<uint2*>(out + (size_t)n * M + m_tile * kTileM + row4) = packed;
     }
+    if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(12);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -654,6 +674,9 @@ cudaError_t launch_by_n(int n_tile, cudaStream_t stream, const CUtensorMap& map,
 extern "C" int fp6b200_debug_read_profile(unsigned long long* host_out) {
     return cudaMemcpyFromSymbol(host_out, g_prof, sizeof(g_prof));
 }
+extern "C" int fp6b200_debug_read_stamps(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_stamp, sizeof(g_stamp));
+}
 #endif
 
 int device_sm_count() {
@@ -712,6 +735,12 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     const int sms = device_sm_count() < (int)kMaxGrid ? device_sm_count() : (int)kMaxGrid;
     Params prm;
     prm.weight = static_cast<const uint8_t*>(weight);
+    {
+        const int bw_ = 1 + e_bits + m_bits;
+        prm.region[0] = prm.weight + region_offset(bw_, 1, M, K);
+        prm.region[1] = prm.weight + region_offset(bw_, 2, M, K);
+        prm.region[2] = prm.weight + region_offset(bw_, 4, M, K);
+    }
     prm.scales = scales;
     prm.out = out;
     prm.workspace = workspace;

@@ -175,6 +175,7 @@ FPX_HD void split_range(uint32_t k_blocks, uint32_t splits, uint32_t z, uint32_t
 //             cover only part of a tile's K range; those go to partial slots 2c and 2c+1 and a fix-up
 //             kernel sums the slots of every split tile in CTA order.
 enum WorkMode : uint32_t { kClassic = 0, kStreamK = 1 };
+constexpr uint32_t kPlanTableGrid = 256;   // largest grid for which a plan carries its table of remainder starts
 enum OutKind : uint32_t { kOutDirect = 0, kOutSplitPartial = 1, kOutSlotPartial = 2 };
 
 struct WorkPlan {
@@ -188,6 +189,10 @@ struct WorkPlan {
     uint32_t full_waves;  // tiles / grid
     uint32_t rem_tiles;   // tiles - full_waves * grid
     uint32_t rem_units32; // rem_tiles * kblocks when (rem_tiles * kblocks + 1) * grid fits 32 bits, else 0
+    // kStreamK, grid <= kPlanTableGrid and kblocks < 65536: rem_start[c] = (remainder tile << 16) | K block at which
+    // CTA c starts in the remainder (c == grid: the end), so that a CTA finds its work with two loads.
+    uint32_t has_table;
+    uint32_t rem_start[kPlanTableGrid + 1];
 };
 
 struct Segment {
@@ -199,11 +204,20 @@ struct Segment {
 };
 
 FPX_HD uint32_t plan_tiles(const WorkPlan& p) { return p.m_tiles * p.n_tiles; }
+FPX_HD uint64_t plan_rem_begin(const WorkPlan& p, uint32_t c);
 FPX_HD void plan_finalize(WorkPlan* p) {
     p->full_waves = plan_tiles(*p) / p->grid;
     p->rem_tiles = plan_tiles(*p) - p->full_waves * p->grid;
     const uint64_t units = (uint64_t)p->rem_tiles * p->kblocks;
     p->rem_units32 = (units + 1) * p->grid <= 0xffffffffull ? (uint32_t)units : 0u;
+    p->has_table = 0;
+    if (p->mode == kStreamK && p->grid <= kPlanTableGrid && p->kblocks < 65536u) {
+        for (uint32_t c = 0; c <= p->grid; c++) {
+            const uint64_t u = plan_rem_begin(*p, c);
+            p->rem_start[c] = ((uint32_t)(u / p->kblocks) << 16) | (uint32_t)(u % p->kblocks);
+        }
+        p->has_table = 1;
+    }
 }
 FPX_HD uint32_t plan_full_waves(const WorkPlan& p) { return p.full_waves; }
 FPX_HD uint32_t plan_rem_tiles(const WorkPlan& p) { return p.rem_tiles; }
@@ -220,19 +234,25 @@ FPX_HD uint32_t plan_rem_owner(const WorkPlan& p, uint64_t u) {
 }
 
 struct SegmentIter {
-    uint32_t step;        // segments handed out so far
-    uint64_t cur, end;    // remainder units still to hand out (kStreamK)
-    uint32_t rem_first;   // 1 until the first remainder segment has been handed out
+    uint32_t step;                 // segments handed out so far
+    uint32_t cur_tile, cur_kb;     // kStreamK: next remainder unit to hand out, as (remainder tile, K block)
+    uint32_t end_tile, end_kb;     // kStreamK: where this CTA's remainder units end
+    uint32_t rem_first;            // 1 until the first remainder segment has been handed out
 };
 
 FPX_HD void plan_start(const WorkPlan& p, uint32_t cta, SegmentIter* it) {
     it->step = 0;
     it->rem_first = 1;
-    if (p.mode == kStreamK) {
-        it->cur = plan_rem_begin(p, cta);
-        it->end = plan_rem_begin(p, cta + 1);
+    it->cur_tile = it->cur_kb = it->end_tile = it->end_kb = 0;
+    if (p.mode != kStreamK) return;
+    if (p.has_table) {
+        const uint32_t a = p.rem_start[cta], b = p.rem_start[cta + 1];
+        it->cur_tile = a >> 16; it->cur_kb = a & 0xffffu;
+        it->end_tile = b >> 16; it->end_kb = b & 0xffffu;
     } else {
-        it->cur = it->end = 0;
+        const uint64_t a = plan_rem_begin(p, cta), b = plan_rem_begin(p, cta + 1);
+        it->cur_tile = (uint32_t)(a / p.kblocks); it->cur_kb = (uint32_t)(a % p.kblocks);
+        it->end_tile = (uint32_t)(b / p.kblocks); it->end_kb = (uint32_t)(b % p.kblocks);
     }
 }
 
@@ -259,11 +279,11 @@ FPX_HD bool plan_next(const WorkPlan& p, uint32_t cta, SegmentIter* it, Segment*
         it->step++;
         return true;
     }
-    if (it->cur >= it->end) return false;
-    const uint32_t kb = (uint32_t)(it->cur % p.kblocks);
-    const uint64_t left = it->end - it->cur;
-    const uint32_t n = (uint32_t)(left < (uint64_t)(p.kblocks - kb) ? left : (uint64_t)(p.kblocks - kb));
-    seg->tile = waves * p.grid + (uint32_t)(it->cur / p.kblocks);
+    if (it->cur_tile == it->end_tile && it->cur_kb >= it->end_kb) return false;
+    if (it->cur_tile > it->end_tile) return false;
+    const uint32_t kb = it->cur_kb;
+    const uint32_t n = (it->cur_tile == it->end_tile ? it->end_kb : p.kblocks) - kb;
+    seg->tile = waves * p.grid + it->cur_tile;
     seg->kb_begin = kb;
     seg->nkb = n;
     if (n == p.kblocks) {
@@ -274,7 +294,9 @@ FPX_HD bool plan_next(const WorkPlan& p, uint32_t cta, SegmentIter* it, Segment*
         seg->out_index = 2 * cta + (it->rem_first ? 0u : 1u);
     }
     it->rem_first = 0;
-    it->cur += n;
+    it->cur_kb = 0;
+    if (kb + n == p.kblocks) it->cur_tile++;
+    else it->cur_kb = kb + n;
     it->step++;
     return true;
 }
@@ -293,6 +315,7 @@ FPX_HD void plan_tile_owners(const WorkPlan& p, uint32_t r, uint32_t* first, uin
 // Slot in which CTA c left its part of remainder tile r (c in [first, last], first != last).  CTAs in
 // that range whose unit range is empty (plan_rem_begin(c) == plan_rem_begin(c+1)) hold nothing.
 FPX_HD uint32_t plan_tile_slot(const WorkPlan& p, uint32_t r, uint32_t c) {
+    if (p.has_table) return ((p.rem_start[c] >> 16) == r) ? 2 * c : 2 * c + 1;
     const uint64_t begin = plan_rem_begin(p, c);
     return (begin / p.kblocks == r) ? 2 * c : 2 * c + 1;
 }
