@@ -174,6 +174,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    torch.set_num_threads(len(os.sched_getaffinity(0)))   # torchrun pins OMP_NUM_THREADS to 1; the baseline gets every core
     e, m, layers, batches = WORKLOADS[args.workload]
     layer = min(layers, key=lambda l: l[1] * l[2])          # the smallest layer of the set
     rows = cpu_sample_rows(e, m, layer, batches, args.steps + args.warmup, budget_s=120.0)
@@ -397,9 +398,20 @@ def run_ours(args):
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_step * args.steps, "clocks": clocks,
             "device_status": status, "cases": per_case,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # Orderly teardown: the graphs hold captured collectives, so they go first; a watchdog ends the process
+        # if the communicator's own teardown does not return.
+        import threading
+        del graphs
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        sys.stdout.flush()
+        watchdog = threading.Timer(20.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
         dist.destroy_process_group()
+        os._exit(0)   # skip interpreter teardown: nothing is left to flush and no destructor may wait on a peer
 
 
 def main():
