@@ -45,9 +45,9 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "llama2-7b-fp6"
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch from an ncu capture, keyed by
-# (workload, layer, batch); see profiles/.  None until a capture exists.
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, averaged over the launches of one step, from the ncu
+# launch list of this command (profiles/launch_list_llama2-7b-fp6_bench_step.md).  A recorded figure, not measured live.
+NCU_TRAFFIC_BYTES = {"llama2-7b-fp6": 38.52e6}
 
 
 def alg_bytes(oc, ic, bs, bw):
@@ -380,7 +380,7 @@ def run_ours(args):
                          f"{batches}: {secs:.2f} s, of which single-threaded dequantisation {deq:.2f} s"}
 
     if rank == 0:
-        traffic = None
+        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if (world == 1 and not args.case) else None
         line = {
             "metric": "w6a16_linear_tflops" if e == 3 else "w5a16_linear_tflops",
             "value": flops_step / sec_step / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -393,7 +393,8 @@ def run_ours(args):
                        "launch": "whole step replayed as a CUDA graph"},
             "weight_gbs": wbytes_step / sec_step / 1e9,
             "roofline": {"bound": "hbm", "achieved": abytes_step / world / sec_step / 1e9, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": abytes_step / world / sec_step / 1e9 / hbm_peak, "traffic": traffic, "peak_source": peak_kind,
+                         "frac": abytes_step / world / sec_step / 1e9 / hbm_peak, "traffic": traffic,
+                         "algorithmic_bytes_per_launch": abytes_step / world / len(cases), "peak_source": peak_kind,
                          "note": "per-GPU algorithmic bytes of all launches of a step / device time of the step; per-case fractions use min(HBM, tensor) roofline"},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_step * args.steps, "clocks": clocks,
             "device_status": status, "cases": per_case,
