@@ -208,7 +208,7 @@ def run_ours(args):
     import torch.distributed as dist
     import fp6_llm_b200 as f
     from fp6_llm_b200.formats import bit_width, synth_layer
-    from fp6_llm_b200.sharding import ShardedFPxLinear, plan_rows
+    from fp6_llm_b200.sharding import PeerExchange, ShardedFPxLinear, plan_rows
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -220,6 +220,9 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     f.lib()   # raises if the CUDA library is missing: there is no fallback
+    # N > 1: the kernel stores its rows into every rank's output buffer (peer-mapped symmetric memory) and ends with an
+    # arrival barrier; --exchange nccl selects one NCCL all-gather per layer instead.
+    exchange = PeerExchange() if (world > 1 and args.exchange == "fused") else None
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
 
     e, m, layers, batches = select_cases(args)
@@ -243,7 +246,8 @@ def run_ours(args):
     replicas = min(48, max(1, -(-target // max(shard_bytes, 1))))
     for mdl in models:
         n_rep = min(64, max(replicas, -(-target // (mdl["packed"].numel() * 4))))
-        mdl["replicas"] = [ShardedFPxLinear(mdl["packed"] if r == 0 else mdl["packed"].clone(), mdl["scale"], mdl["plan"], rank, e, m)
+        mdl["replicas"] = [ShardedFPxLinear(mdl["packed"] if r == 0 else mdl["packed"].clone(), mdl["scale"], mdl["plan"], rank, e, m,
+                                            exchange=exchange)
                            for r in range(n_rep)]
     acts = {(mdl["name"], bs): torch.randn(bs, mdl["ic"], device=dev, dtype=torch.float16) for mdl in models for bs in batches}
     cases = [(mdl, bs) for bs in batches for mdl in models]
@@ -309,7 +313,8 @@ def run_ours(args):
     wbytes_step = sum(mdl["oc"] * mdl["ic"] * bw / 8 for mdl, bs in cases)
     abytes_step = sum(alg_bytes(mdl["oc"], mdl["ic"], bs, bw) for mdl, bs in cases)
     sec_step = ms_total / 1e3 / args.steps
-    launches_step = sum(1 + (1 if split[(mdl["name"], bs)] != 1 else 0) for mdl, bs in cases)   # GEMM + reduce/fix-up
+    launches_step = sum(1 + (1 if split[(mdl["name"], bs)] != 1 else 0) + (1 if exchange is not None else 0)
+                        for mdl, bs in cases)   # GEMM + reduce/fix-up (+ arrival barrier)
     hbm_peak, tc_peak, peak_kind = peaks()
 
     # ---- per-case device times (separate pass, each case alone in a graph of `replicas` launches)
@@ -388,7 +393,9 @@ def run_ours(args):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": args.workload + (f" [{args.case} only]" if args.case else ""), "format": f"e{e}m{m}", "layers": [list(l) for l in layers], "batch_sizes": batches,
                        "split_k": "0 (library: tile waves + stream-K remainder)" if args.split_k <= 0 else args.split_k,
-                       "parallelism": "single GPU" if world == 1 else f"OC-sharded x{world} + all-gather of [BS, OC]",
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"OC-sharded x{world}, rows stored into every rank's [BS, OC] by the kernel over NVLink + arrival barrier" if exchange is not None
+                           else f"OC-sharded x{world} + NCCL all-gather of [BS, OC]"),
                        "l2": f"inputs larger than L2: {replicas} replicas of the layer set ({shard_bytes * replicas / 2**20:.0f} MiB) rotated so a buffer is re-read only after >= 512 MiB of other weights",
                        "launch": "whole step replayed as a CUDA graph"},
             "weight_gbs": wbytes_step / sec_step / 1e9,
@@ -424,6 +431,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--split-k", type=int, default=0, help="0 = let the library decompose the work")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused", help="N > 1: how the ranks' rows reach each other")
     ap.add_argument("--case", default=None, help="LAYER:BATCH - run only this launch shape of the workload (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -27,6 +27,7 @@ C_SYMBOLS = (
     "fp6b200_workspace_bytes", "fp6b200_choose_split_k", "fp6b200_prepack", "fp6b200_prepack_host",
     "fp6b200_dequant", "fp6b200_dequant_host", "fp6b200_dequant_packed", "fp6b200_splitk_reduce",
     "fp6b200_device_status", "fp6b200_linear_static_scratch", "fp6b200_static_scratch_bytes",
+    "fp6b200_linear_gather",
 )
 
 
@@ -103,6 +104,8 @@ def lib() -> ctypes.CDLL:
     L.fp6b200_linear_static_scratch.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz]
     L.fp6b200_static_scratch_bytes.restype = sz
     L.fp6b200_static_scratch_bytes.argtypes = []
+    L.fp6b200_linear_gather.restype = ci
+    L.fp6b200_linear_gather.argtypes = [ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, ci, sz, sz, sz, sz, sz, vp, ci]
     L.fp6b200_device_status.restype = ci
     L.fp6b200_device_status.argtypes = [ctypes.POINTER(ci)]
     _lib = L

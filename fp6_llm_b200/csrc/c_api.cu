@@ -121,6 +121,34 @@ int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_pack
                             static_cast<__half*>(out), M, N, K, workspace, split_k, status);
 }
 
+int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weight_shard, const void* scales_shard,
+                          const void* act, void* const* out_peers, void* const* flag_peers, void* epoch_counter, int world,
+                          int rank, size_t out_rows, size_t row0, size_t M, size_t N, size_t K, float* workspace,
+                          int split_k) {
+    int* status = status_ptr();
+    if (!status) return cudaErrorInitializationError;
+    if (!out_peers || !flag_peers || world < 1 || world > fpx::kMaxOutTargets || rank < 0 || rank >= world)
+        return cudaErrorInvalidValue;
+    if (out_rows > 0x7fffffffull || row0 > 0x7fffffffull || row0 + M > out_rows || out_rows % 4 != 0 || row0 % 4 != 0)
+        return cudaErrorInvalidValue;
+    if (split_k != 0 && split_k != 1) return cudaErrorInvalidValue;
+    fpx::OutTargets targets = {};
+    uint32_t* flags[fpx::kMaxOutTargets] = {};
+    for (int r = 0; r < world; r++) {
+        targets.ptr[r] = static_cast<__half*>(out_peers[r]);
+        flags[r] = static_cast<uint32_t*>(flag_peers[r]);
+    }
+    targets.count = (uint32_t)world;
+    targets.ld = (uint32_t)out_rows;
+    targets.row0 = (uint32_t)row0;
+    cudaError_t err = fpx::launch_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_shard,
+                                       static_cast<const __half*>(scales_shard), static_cast<const __half*>(act), nullptr,
+                                       M, N, K, workspace, split_k, status, &targets);
+    if (err != cudaSuccess) return err;
+    return fpx::launch_gather_barrier(static_cast<cudaStream_t>(stream), flags, world, rank,
+                                      static_cast<uint32_t*>(epoch_counter), status);
+}
+
 int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev, const void* scales_dev,
                            const void* act_host, void* out_host, size_t M, size_t N, size_t K, int split_k) {
     if (!act_host || !out_host || split_k < 0) return cudaErrorInvalidValue;

@@ -60,7 +60,7 @@ constexpr uint32_t kTmemCols = 512;      // the whole tensor memory: one CTA per
 // status codes written by a wait that gave up
 enum : int {
     kErrStageEmpty = 1, kErrStageFull = 2, kErrAEmpty = 3, kErrAFull = 6, kErrAccFull = 7, kErrSmemAlign = 8,
-    kErrAccEmpty = 9
+    kErrAccEmpty = 9, kErrPeerWait = 10   // 10: a peer GPU did not arrive at the end of a sharded layer
 };
 
 // Packed bytes of one (64 rows x 64 K) block per segment width.
@@ -138,7 +138,7 @@ struct Params {
     const uint8_t* weight;
     const uint8_t* region[3];   // start of the 1-bit, 2-bit and 4-bit regions of the packed weights
     const __half* scales;
-    __half* out;
+    OutTargets out;             // where finished fp16 tiles go (this GPU's buffer, or every rank's)
     float* workspace;
     uint32_t M, N, K;
     WorkPlan plan;
@@ -384,10 +384,16 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                         for (int u = 0; u < CH; u++) f[u] += __uint_as_float(v[u]);
                     }
                 if (seg.out_kind == kOutDirect) {
-                    __half* dst = p.out + (size_t)n0 * p.M + row;
 #pragma unroll
-                    for (int u = 0; u < CH; u++)
-                        if (n0 + u < p.N) dst[(size_t)u * p.M] = __float2half_rn(f[u] * row_scale);
+                    for (int u = 0; u < CH; u++) f[u] *= row_scale;
+                    const size_t first = (size_t)n0 * p.out.ld + p.out.row0 + row;
+#pragma unroll 1
+                    for (uint32_t r = 0; r < p.out.count; r++) {   // one target, or the buffer of every rank
+                        __half* dst = p.out.ptr[r] + first;
+#pragma unroll
+                        for (int u = 0; u < CH; u++)
+                            if (n0 + u < p.N) dst[(size_t)u * p.out.ld] = __float2half_rn(f[u]);
+                    }
                 } else if (seg.out_kind == kOutSplitPartial) {
                     float* dst = p.workspace + ((size_t)seg.out_index * p.N + n0) * p.M + row;
 #pragma unroll
@@ -557,8 +563,8 @@ constexpr int kFixupCols = 16;
 #define FPX_EVEN_PCT 85
 #endif
 constexpr uint64_t kEvenGridMinPercent = FPX_EVEN_PCT;
-__global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(__half* __restrict__ out, const float* __restrict__ slots,
-                                                                         uint32_t M, uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan) {
+__global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
+                                                                         uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
@@ -602,9 +608,43 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(__half* 
         uint2 packed;
         packed.x = *reinterpret_cast<uint32_t*>(&lo);
         packed.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(out + (size_t)n * M + m_tile * kTileM + row4) = packed;
+        const size_t at = (size_t)n * out.ld + out.row0 + m_tile * kTileM + row4;
+        for (uint32_t t = 0; t < out.count; t++) *reinterpret_cast<uint2*>(out.ptr[t] + at) = packed;
     }
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(12);
+}
+
+// Arrival barrier between the GPUs of an OC-sharded layer.  Thread r tells rank r "the rows of rank `rank` are in
+// your buffer" (a release store of this call's number to word `rank` of r's flag array) and then waits until rank r
+// has said the same here (word r of the own array).  The call number lives in device memory and is advanced by the
+// kernel itself, so a replayed CUDA graph keeps counting.  The kernels before it on the stream have completed when
+// it runs (stream order, or griddepcontrol.wait under programmatic launch), which is what makes this rank's stores
+// to the peers complete.  The wait is bounded: after kPeerWaitNs the kernel records kErrPeerWait and returns.
+struct PeerFlags {
+    uint32_t* ptr[kMaxOutTargets];
+};
+constexpr unsigned long long kPeerWaitNs = 2000000000ull;
+__global__ void __launch_bounds__(32) gather_barrier_kernel(const __grid_constant__ PeerFlags flags, int world, int rank,
+                                                            uint32_t* epoch_counter, int* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int r = (int)threadIdx.x;
+    const uint32_t epoch = *epoch_counter + 1u;
+    __syncwarp();
+    if (r == 0) *epoch_counter = epoch;
+    if (r >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.ptr[r] + rank), "r"(epoch) : "memory");
+    const uint32_t* mine = flags.ptr[rank] + r;
+    const unsigned long long t0 = ptx::global_timer_ns();
+    for (uint32_t polls = 0;; polls++) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if ((int32_t)(seen - epoch) >= 0) break;
+        if ((polls & 63u) == 63u && ptx::global_timer_ns() - t0 > kPeerWaitNs) {
+            atomicCAS(status, 0, kErrPeerWait);
+            break;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -716,8 +756,24 @@ cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* 
 
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
-                        int* status) {
+                        int* status, const OutTargets* targets) {
     if (!format_supported(e_bits, m_bits)) return cudaErrorInvalidValue;
+    OutTargets where;
+    if (targets) {
+        where = *targets;
+        if (where.count == 0 || where.count > (uint32_t)kMaxOutTargets || split_k > 1) return cudaErrorInvalidValue;
+        if (where.ld % 4 != 0 || where.row0 % 4 != 0 || (size_t)where.row0 + M > where.ld) return cudaErrorInvalidValue;
+        for (uint32_t t = 0; t < where.count; t++) {
+            if (!where.ptr[t]) return cudaErrorInvalidValue;
+            if (reinterpret_cast<uintptr_t>(where.ptr[t]) & 7) return cudaErrorMisalignedAddress;
+        }
+        out = where.ptr[0];
+    } else {
+        where.ptr[0] = out;
+        where.count = 1;
+        where.ld = (uint32_t)M;
+        where.row0 = 0;
+    }
     if (M == 0 || M % 256 != 0 || K == 0 || K % 64 != 0 || N == 0 || split_k < 0 || split_k > 65535)
         return cudaErrorInvalidValue;
     if (!weight || !scales || !act || !out || (split_k != 1 && !workspace)) return cudaErrorInvalidValue;
@@ -742,7 +798,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         prm.region[2] = prm.weight + region_offset(bw_, 4, M, K);
     }
     prm.scales = scales;
-    prm.out = out;
+    prm.out = where;
     prm.workspace = workspace;
     prm.M = (uint32_t)M;
     prm.N = (uint32_t)N;
@@ -788,10 +844,31 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, out, (const float*)workspace, (uint32_t)M, (uint32_t)N, n_tile, plan);
+        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan);
     }
     if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true);
     return cudaSuccess;
+}
+
+cudaError_t launch_gather_barrier(cudaStream_t stream, uint32_t* const* flag_peers, int world, int rank,
+                                  uint32_t* epoch_counter, int* status) {
+    if (!flag_peers || world < 1 || world > kMaxOutTargets || rank < 0 || rank >= world || !epoch_counter || !status)
+        return cudaErrorInvalidValue;
+    PeerFlags flags = {};
+    for (int r = 0; r < world; r++) {
+        if (!flag_peers[r] || (reinterpret_cast<uintptr_t>(flag_peers[r]) & 3)) return cudaErrorInvalidValue;
+        flags.ptr[r] = flag_peers[r];
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_barrier_kernel, flags, world, rank, epoch_counter, status);
 }
 
 }  // namespace fpx

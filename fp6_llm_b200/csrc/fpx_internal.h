@@ -10,10 +10,27 @@ namespace fpx {
 // Only e3m2 (FP6) and e2m2 (FP5) exist in the reference (fp6_llm/csrc/fp6_linear.cu:133-138).
 inline bool format_supported(int e_bits, int m_bits) { return m_bits == 2 && (e_bits == 3 || e_bits == 2); }
 
-// GEMM (+ split-K reduction when split_k > 1).  All pointers are device pointers.
+// Where the fp16 result goes.  One target with ld == M and row0 == 0 is the plain layer.  Several targets are the
+// output buffers [N][ld] of the ranks of an OC-sharded layer (this GPU's and its peers', as mapped into this
+// process): the M rows computed here are stored at rows row0 .. row0 + M of every target.
+constexpr int kMaxOutTargets = 8;
+struct OutTargets {
+    __half* ptr[kMaxOutTargets];
+    uint32_t count;
+    uint32_t ld;
+    uint32_t row0;
+};
+
+// GEMM (+ split-K reduction when split_k > 1).  All pointers are device pointers.  targets == nullptr: the result
+// goes to out[N][M]; otherwise out is ignored (split_k must then be 0 or 1).
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
-                        int* status);
+                        int* status, const OutTargets* targets = nullptr);
+// Cross-GPU arrival barrier that ends a sharded layer: tells every peer that this rank's stores into its output
+// buffer are complete and waits (bounded) for the same word from every peer.  flag_peers[r] = rank r's flag array
+// (one 32-bit word per rank) as mapped here; epoch_counter = this rank's own call counter in device memory.
+cudaError_t launch_gather_barrier(cudaStream_t stream, uint32_t* const* flag_peers, int world, int rank,
+                                  uint32_t* epoch_counter, int* status);
 cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k,
                                  bool after_gemm = false);
 int gemm_n_tile(size_t N);

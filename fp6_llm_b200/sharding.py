@@ -1,8 +1,14 @@
 """Output-channel (column-parallel) sharding of one FPx linear layer across the GPUs of a node.
 
-Rank r owns a contiguous range of output channels, computes Out[:, r0:r1] with the single-GPU kernel and
-the ranks exchange their column slabs with ONE all-gather (torch.distributed; NCCL over NVLink on GPUs, gloo
-in the CPU tests).  The reference has no multi-GPU code at all; the one thing that comes from it is the packed
+Rank r owns a contiguous range of output channels and computes Out[:, r0:r1] with the single-GPU kernel.  The
+column slabs reach the other ranks in one of two ways:
+
+  * fused (PeerExchange): the kernel's epilogue stores every finished tile straight into the output buffer of
+    EVERY rank (peer-mapped symmetric memory, plain stores over NVLink) and a one-warp kernel ends the layer with
+    an arrival barrier between the GPUs.  No separate collective, no staging copy.
+  * ONE all-gather (torch.distributed; NCCL over NVLink on GPUs, gloo in the CPU tests) of the per-rank slabs.
+
+The reference has no multi-GPU code at all; the one thing that comes from it is the packed
 layout, which decides how a shard must be cut:
 
     the packed tensor is [1-bit region][2-bit region][4-bit region] over the WHOLE matrix
@@ -12,6 +18,7 @@ layout, which decides how a shard must be cut:
 """
 from __future__ import annotations
 
+import ctypes
 from typing import List, Sequence, Tuple
 
 import torch
@@ -81,20 +88,102 @@ def gather_columns(local: torch.Tensor, plan: Sequence[Tuple[int, int]], rank: i
     return torch.cat([gathered[r, :, : widths[r]] for r in range(world)], dim=1)
 
 
+class PeerExchange:
+    """What the ranks of one process group share for the fused exchange: a flag word per pair of ranks, this rank's
+    call counter, and two alternating output buffers per (batch, out_channels) shape, all but the counter in symmetric
+    memory (torch.distributed._symmetric_memory: every rank's allocation is mapped into every process).
+
+    A rank can run at most one layer ahead of a peer (each layer ends with the arrival barrier), so a result stays
+    valid until the second next layer of the same shape is started on this rank: consume it (on the same stream)
+    before that, or copy it."""
+
+    MAX_WORLD = 8
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > self.MAX_WORLD:
+            raise ValueError(f"the fused exchange handles at most {self.MAX_WORLD} ranks")
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._symm = symm
+        self.flags = symm.empty(64, dtype=torch.int32, device=self.device)
+        self._flags_handle = symm.rendezvous(self.flags, self.group)
+        self.flags.zero_()
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)          # nobody signals before every rank has cleared its flags
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._flags_handle.buffer_ptrs])
+        self._buffers = {}
+
+    def _next_buffer(self, batch: int, out_channels: int):
+        key = (batch, out_channels)
+        slot = self._buffers.get(key)
+        if slot is None:
+            pair = []
+            for _ in range(2):
+                t = self._symm.empty((batch, out_channels), dtype=torch.float16, device=self.device)
+                h = self._symm.rendezvous(t, self.group)
+                pair.append((t, h, (ctypes.c_void_p * self.world)(*[int(p) for p in h.buffer_ptrs])))
+            slot = {"pair": pair, "next": 0}
+            self._buffers[key] = slot
+        entry = slot["pair"][slot["next"]]
+        slot["next"] ^= 1
+        return entry
+
+    def reserve(self, batch: int, out_channels: int) -> None:
+        """Creates the output buffers of a shape now (a collective call: every rank, same order)."""
+        key = (batch, out_channels)
+        if key not in self._buffers:
+            self._next_buffer(batch, out_channels)
+            self._buffers[key]["next"] = 0
+
+    def linear(self, layer: "ShardedFPxLinear", x: torch.Tensor, split_k: int = 0) -> torch.Tensor:
+        """The whole [B, OC] result of the sharded layer on this rank (a view of an exchange buffer)."""
+        from . import _native
+        from .ops import _ptr, _stream_ptr, _workspace
+        if split_k not in (0, 1):
+            raise ValueError("the fused exchange takes split_k 0 or 1")
+        if x.dtype != torch.float16 or not x.is_cuda or x.dim() != 2 or not x.is_contiguous():
+            raise ValueError("activations must be a contiguous fp16 CUDA tensor [B, IC]")
+        if len(layer.plan) != self.world or layer.rank != self.rank:
+            raise ValueError("the layer's plan does not match this process group")
+        batch, ic = x.shape
+        r0, r1 = layer.plan[self.rank]
+        oc = layer.plan[-1][1]
+        if layer.packed.shape[0] != r1 - r0 or layer.packed.shape[1] * 32 != ic * bit_width(layer.e_bits, layer.m_bits):
+            raise ValueError("packed shard does not match the plan or the activations")
+        out, _handle, out_ptrs = self._next_buffer(batch, oc)
+        L = _native.lib()
+        with torch.cuda.device(self.device):
+            nbytes = L.fp6b200_workspace_bytes(r1 - r0, batch, ic, split_k)
+            ws = _workspace(self.device, nbytes) if nbytes else None
+            rc = L.fp6b200_linear_gather(layer.e_bits, layer.m_bits, _stream_ptr(self.device), _ptr(layer.packed),
+                                         _ptr(layer.scale), _ptr(x), out_ptrs, self._flag_ptrs, _ptr(self.epoch),
+                                         self.world, self.rank, oc, r0, r1 - r0, batch, ic,
+                                         _ptr(ws) if ws is not None else None, split_k)
+        _native.check(rc, "fp6b200_linear_gather")
+        return out
+
+
 class ShardedFPxLinear:
-    """One rank's part of an OC-sharded FPx linear layer.  `packed_shard`/`scale_shard` live on this rank's GPU."""
+    """One rank's part of an OC-sharded FPx linear layer.  `packed_shard`/`scale_shard` live on this rank's GPU.
+    With `exchange` (a PeerExchange) the slabs are exchanged by the kernel itself, otherwise by one all-gather."""
 
     def __init__(self, packed_shard: torch.Tensor, scale_shard: torch.Tensor, plan: Sequence[Tuple[int, int]],
-                 rank: int, e_bits: int = 3, m_bits: int = 2, group=None):
+                 rank: int, e_bits: int = 3, m_bits: int = 2, group=None, exchange: "PeerExchange | None" = None):
         self.packed, self.scale, self.plan, self.rank = packed_shard, scale_shard, list(plan), rank
-        self.e_bits, self.m_bits, self.group = e_bits, m_bits, group
+        self.e_bits, self.m_bits, self.group, self.exchange = e_bits, m_bits, group, exchange
 
     def forward_local(self, x: torch.Tensor, split_k: int = 0) -> torch.Tensor:
         from .ops import linear_forward_eXmY_cuda
         return linear_forward_eXmY_cuda(self.e_bits, self.m_bits, x, self.packed, self.scale, split_k)
 
     def forward(self, x: torch.Tensor, split_k: int = 0) -> torch.Tensor:
-        y = self.forward_local(x, split_k)
         if len(self.plan) == 1:
-            return y
-        return gather_columns(y, self.plan, self.rank, self.group)
+            return self.forward_local(x, split_k)
+        if self.exchange is not None:
+            return self.exchange.linear(self, x, split_k)
+        return gather_columns(self.forward_local(x, split_k), self.plan, self.rank, self.group)

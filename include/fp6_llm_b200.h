@@ -117,6 +117,25 @@ int fp6b200_linear_static_scratch(int e_bits, int m_bits, void* stream, const vo
 size_t fp6b200_static_scratch_bytes(void);
 
 /*
+ * One rank's part of an OC-sharded linear layer with the exchange fused in (no counterpart in the reference, which
+ * is single-GPU: fp6_llm/csrc/fp6_linear.cu:104-139 computes the whole layer on one device).  This rank holds the
+ * packed shard of M output channels (rows row0 .. row0 + M of the layer's out_rows channels) and the matching scales;
+ * act is the full [N][K] activation.  The kernel stores its [N][M] result straight into rows row0.. of EVERY rank's
+ * output buffer [N][out_rows] (out_peers[r] = rank r's buffer as mapped into this process, peer-to-peer over
+ * NVLink; out_peers[rank] is the local one), then tells every peer that its rows are there and waits for theirs:
+ * flag_peers[r] = rank r's array of `world` 32-bit words, zeroed once before the first call; epoch_counter = a 32-bit
+ * word in this rank's own memory, zeroed once, advanced by each call on the device.  When the call has completed on
+ * the stream, out_peers[rank] holds the whole [N][out_rows] result.  Every rank must make the same sequence of calls.
+ * A rank may be one call ahead of a peer, so successive calls must alternate between two output buffers.
+ * split_k: 0 (library decomposition) or 1.  workspace as for fp6b200_linear.  A peer that does not arrive within two
+ * seconds ends the wait; fp6b200_device_status then reports code 10 and the output is incomplete.
+ */
+int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weight_shard, const void* scales_shard,
+                          const void* act, void* const* out_peers, void* const* flag_peers, void* epoch_counter, int world,
+                          int rank, size_t out_rows, size_t row0, size_t M, size_t N, size_t K, float* workspace,
+                          int split_k);
+
+/*
  * Synchronises the current device, returns in *code the first time-out code a GEMM CTA recorded
  * since the last call (0 = none) and clears it.  A non-zero code means a bounded wait inside the
  * kernel gave up and the output of that launch is invalid.
