@@ -228,8 +228,8 @@ def run_ours(args):
     e, m, layers, batches = select_cases(args)
     bw = bit_width(e, m)
     # ---- weights: seeded N(0, 0.02) -> per-row scale -> round-to-nearest codes -> GPU prepack; replicas for cold L2
-    shard_bytes = 0
-    models = []          # per layer: dict(name, oc, ic, plan, replicas=[ShardedFPxLinear...])
+    shard_bytes = 0      # of the LARGEST shard of every layer: replica counts must be the same on every rank, because
+    models = []          # every rank has to make the same sequence of layer calls          # per layer: dict(name, oc, ic, plan, replicas=[ShardedFPxLinear...])
     for li, (name, oc, ic) in enumerate(layers):
         plan = plan_rows(oc, world)
         r0, r1 = plan[rank]
@@ -237,15 +237,16 @@ def run_ours(args):
         w, s = w[r0:r1].contiguous(), s[r0:r1].contiguous()
         packed = f.weight_prepacking_eXmY_cpu(e, m, w)
         del w
-        shard_bytes += packed.numel() * 4
-        models.append({"name": name, "oc": oc, "ic": ic, "plan": plan, "packed": packed, "scale": s})
+        widest = max(b - a for a, b in plan) * ic * bw // 8
+        shard_bytes += widest
+        models.append({"name": name, "oc": oc, "ic": ic, "plan": plan, "packed": packed, "scale": s, "widest": widest})
     # Cold-L2 protocol: a (layer, replica) buffer is re-read only after >= 512 MiB of other weights went by.
     # In the step graph batch index bi of step s uses replica (s*len(batches)+bi) % replicas of every layer;
     # the per-case pass below rotates over enough replicas of that one layer.
     target = 512 * 1024 * 1024
     replicas = min(48, max(1, -(-target // max(shard_bytes, 1))))
     for mdl in models:
-        n_rep = min(64, max(replicas, -(-target // (mdl["packed"].numel() * 4))))
+        n_rep = min(64, max(replicas, -(-target // mdl["widest"])))
         mdl["replicas"] = [ShardedFPxLinear(mdl["packed"] if r == 0 else mdl["packed"].clone(), mdl["scale"], mdl["plan"], rank, e, m,
                                             exchange=exchange)
                            for r in range(n_rep)]

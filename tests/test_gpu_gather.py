@@ -109,10 +109,12 @@ def test_gather_rejects_bad_arguments(native_lib):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_processes_two_gpus():
-    """One process per GPU: symmetric-memory buffers, peer stores over NVLink, the barrier between real ranks."""
+def test_one_process_per_gpu():
+    """One process per GPU (2, 4 or 8 of them): symmetric-memory buffers, peer stores over NVLink, the barrier
+    between real ranks."""
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+    ranks = max(n for n in (2, 4, 8) if n <= torch.cuda.device_count())
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(ROOT, "tests", "gather_worker.py")]
     done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-4000:]
