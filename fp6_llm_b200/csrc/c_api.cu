@@ -141,10 +141,12 @@ int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weig
     targets.count = (uint32_t)world;
     targets.ld = (uint32_t)out_rows;
     targets.row0 = (uint32_t)row0;
-    fpx::PeerArrival arrival = {flags, static_cast<uint32_t*>(epoch_counter), world, rank};
-    return fpx::launch_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_shard,
-                            static_cast<const __half*>(scales_shard), static_cast<const __half*>(act), nullptr, M, N, K,
-                            workspace, split_k, status, &targets, &arrival);
+    cudaError_t err = fpx::launch_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_shard,
+                                       static_cast<const __half*>(scales_shard), static_cast<const __half*>(act), nullptr,
+                                       M, N, K, workspace, split_k, status, &targets);
+    if (err != cudaSuccess) return err;
+    return fpx::launch_gather_barrier(static_cast<cudaStream_t>(stream), flags, world, rank,
+                                      static_cast<uint32_t*>(epoch_counter), status);
 }
 
 int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev, const void* scales_dev,

@@ -26,7 +26,6 @@
 // Every mbarrier wait is bounded; on a time-out the CTA records a code in a status word, drains its
 // own copies, frees its tensor memory and returns.
 #include <cuda.h>
-#include <mutex>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -553,45 +552,6 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
     *reinterpret_cast<uint2*>(out + i) = packed;
 }
 
-// Arrival barrier between the GPUs of an OC-sharded layer.  Thread r (of the first warp) tells rank r "the rows of
-// rank `rank` are in your buffer" (a release store of this call's number to word `rank` of r's flag array) and then
-// waits until rank r has said the same here (word r of the own array).  The call number lives in device memory and
-// is advanced on the device, so a replayed CUDA graph keeps counting.  The caller guarantees that every store of
-// this rank to the peers happens before the call (kernel boundary, or fences plus a counter of finished CTAs).
-// The wait is bounded: after kPeerWaitNs the thread records kErrPeerWait and returns.
-struct PeerSync {
-    uint32_t* flags[kMaxOutTargets];   // flags[r] = rank r's flag array as mapped here
-    uint32_t* epoch_counter;           // this rank's call counter
-    uint32_t* done_counter;            // CTAs of the fix-up kernel that have finished (reset by the last one)
-    int* status;
-    int world;                         // 0: no barrier
-    int rank;
-};
-constexpr unsigned long long kPeerWaitNs = 2000000000ull;
-__device__ __forceinline__ void peer_arrive_and_wait(const PeerSync& sync, int r) {
-    const uint32_t epoch = *sync.epoch_counter + 1u;
-    __syncwarp();
-    if (r == 0) *sync.epoch_counter = epoch;
-    if (r >= sync.world) return;
-    __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(sync.flags[r] + sync.rank), "r"(epoch) : "memory");
-    const uint32_t* mine = sync.flags[sync.rank] + r;
-    const unsigned long long t0 = ptx::global_timer_ns();
-    for (uint32_t polls = 0;; polls++) {
-        uint32_t seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-        if ((int32_t)(seen - epoch) >= 0) break;
-        if ((polls & 63u) == 63u && ptx::global_timer_ns() - t0 > kPeerWaitNs) {
-            atomicCAS(sync.status, 0, kErrPeerWait);
-            break;
-        }
-    }
-}
-__global__ void __launch_bounds__(32) gather_barrier_kernel(const __grid_constant__ PeerSync sync) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    peer_arrive_and_wait(sync, (int)threadIdx.x);
-}
-
 // Fix-up of the stream-K remainder: CTA = (remainder tile, group of kFixupCols token columns); a thread owns four
 // consecutive output channels of one token column (32 threads per column).  Sums, in CTA order, the partial slots of every
 // CTA that worked on the tile (fp32, float4 loads) and stores fp16; tiles that one CTA computed alone were stored
@@ -603,13 +563,9 @@ constexpr int kFixupCols = 16;
 #define FPX_EVEN_PCT 85
 #endif
 constexpr uint64_t kEvenGridMinPercent = FPX_EVEN_PCT;
-#ifndef FPX_MIN_UNITS
-#define FPX_MIN_UNITS 8
-#endif
-constexpr uint64_t kMinUnitsPerCta = FPX_MIN_UNITS;   // a CTA is not started for fewer 64-K blocks than this
+constexpr uint64_t kMinUnitsPerCta = 8;   // a CTA is not started for fewer 64-K blocks than this (two 256-K stages)
 __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
-                                                                         uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan,
-                                                                         const __grid_constant__ PeerSync sync) {
+                                                                         uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
@@ -617,10 +573,10 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(10);
     uint32_t first, last;
     plan_tile_owners(plan, r, &first, &last);
-    if (first == last && sync.world == 0) return;
+    if (first == last) return;
     const uint32_t tile = plan_full_waves(plan) * plan.grid + r;
     const uint32_t m_tile = tile / plan.n_tiles, n_tile = tile % plan.n_tiles;
-    const uint32_t span = first == last ? 0u : (last - first + 1 < kMaxGrid ? last - first + 1 : kMaxGrid);
+    const uint32_t span = last - first + 1 < kMaxGrid ? last - first + 1 : kMaxGrid;
     for (uint32_t i = threadIdx.x; i < span; i += blockDim.x) {   // one candidate CTA per thread
         const uint32_t cta = first + i;
         const bool holds = plan_rem_begin(plan, cta) != plan_rem_begin(plan, cta + 1);
@@ -641,7 +597,7 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(11);
     const uint32_t c = blockIdx.y * kFixupCols + (threadIdx.x >> 5);
     const uint32_t n = n_tile * n_tile_size + c;
-    if (first != last && c < (uint32_t)n_tile_size && n < N) {
+    if (c < (uint32_t)n_tile_size && n < N) {
         const float* base = slots + (size_t)c * kTileM + row4;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
@@ -657,23 +613,39 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __
         for (uint32_t t = 0; t < out.count; t++) *reinterpret_cast<uint2*>(out.ptr[t] + at) = packed;
     }
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(12);
-    if (sync.world > 0) {
-        // Sharded layer: the CTA that finishes last tells the peers and waits for them.  Every thread orders its own
-        // stores (some went to peer memory) before the CTA is counted as finished; the GEMM's direct stores were
-        // complete before griddepcontrol.wait returned.
-        __shared__ uint32_t is_last;
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const uint32_t total = gridDim.x * gridDim.y;
-            const uint32_t prev = atomicAdd(sync.done_counter, 1u);
-            is_last = prev + 1u == total ? 1u : 0u;
-            if (is_last) *sync.done_counter = 0u;   // nobody else touches it until the next launch
-        }
-        __syncthreads();
-        if (is_last && threadIdx.x < 32) {
-            __threadfence();
-            peer_arrive_and_wait(sync, (int)threadIdx.x);
+}
+
+// Arrival barrier between the GPUs of an OC-sharded layer.  Thread r tells rank r "the rows of rank `rank` are in
+// your buffer" (a release store of this call's number to word `rank` of r's flag array) and then waits until rank r
+// has said the same here (word r of the own array).  The call number lives in device memory and is advanced by the
+// kernel itself, so a replayed CUDA graph keeps counting.  The kernels before it on the stream have completed when
+// it runs (stream order, or griddepcontrol.wait under programmatic launch), which is what makes this rank's stores
+// to the peers complete.  The wait is bounded: after kPeerWaitNs the kernel records kErrPeerWait and returns.
+// (Running this in the last CTA of the fix-up kernel instead, behind a system-scope fence and a counter of finished
+// CTAs, was measured 6 us slower per layer on two GPUs than this separate one-warp launch.)
+struct PeerFlags {
+    uint32_t* ptr[kMaxOutTargets];
+};
+constexpr unsigned long long kPeerWaitNs = 2000000000ull;
+__global__ void __launch_bounds__(32) gather_barrier_kernel(const __grid_constant__ PeerFlags flags, int world, int rank,
+                                                            uint32_t* epoch_counter, int* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int r = (int)threadIdx.x;
+    const uint32_t epoch = *epoch_counter + 1u;
+    __syncwarp();
+    if (r == 0) *epoch_counter = epoch;
+    if (r >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.ptr[r] + rank), "r"(epoch) : "memory");
+    const uint32_t* mine = flags.ptr[rank] + r;
+    const unsigned long long t0 = ptx::global_timer_ns();
+    for (uint32_t polls = 0;; polls++) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if ((int32_t)(seen - epoch) >= 0) break;
+        if ((polls & 63u) == 63u && ptx::global_timer_ns() - t0 > kPeerWaitNs) {
+            atomicCAS(status, 0, kErrPeerWait);
+            break;
         }
     }
 }
@@ -785,55 +757,10 @@ cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* 
     return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, out, partials, elems, split_k);
 }
 
-// Counter of finished fix-up CTAs of a sharded layer (one per device; the launches that use it are ordered on a stream).
-__device__ uint32_t g_fixup_done;
-static uint32_t* fixup_done_counter() {
-    static std::mutex mu;
-    static uint32_t* addr[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!addr[dev]) {
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_fixup_done) != cudaSuccess) return nullptr;
-        addr[dev] = static_cast<uint32_t*>(p);
-    }
-    return addr[dev];
-}
-
-static cudaError_t launch_gather_barrier(cudaStream_t stream, const PeerSync& sync) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1);
-    cfg.blockDim = dim3(32);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gather_barrier_kernel, sync);
-}
-
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
-                        int* status, const OutTargets* targets, const PeerArrival* arrival) {
+                        int* status, const OutTargets* targets) {
     if (!format_supported(e_bits, m_bits)) return cudaErrorInvalidValue;
-    PeerSync sync = {};
-    if (arrival) {
-        if (!targets || !arrival->flag_peers || arrival->world < 1 || arrival->world > kMaxOutTargets ||
-            arrival->rank < 0 || arrival->rank >= arrival->world || !arrival->epoch_counter)
-            return cudaErrorInvalidValue;
-        for (int r = 0; r < arrival->world; r++) {
-            if (!arrival->flag_peers[r] || (reinterpret_cast<uintptr_t>(arrival->flag_peers[r]) & 3)) return cudaErrorInvalidValue;
-            sync.flags[r] = arrival->flag_peers[r];
-        }
-        sync.epoch_counter = arrival->epoch_counter;
-        sync.done_counter = fixup_done_counter();
-        if (!sync.done_counter) return cudaErrorInitializationError;
-        sync.status = status;
-        sync.world = arrival->world;
-        sync.rank = arrival->rank;
-    }
     OutTargets where;
     if (targets) {
         where = *targets;
@@ -913,7 +840,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     if (err != cudaSuccess) return err;
     if (plan.mode == kStreamK) {
         const uint32_t rem = plan_rem_tiles(plan);
-        if (rem == 0) return sync.world ? launch_gather_barrier(stream, sync) : cudaSuccess;
+        if (rem == 0) return cudaSuccess;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(rem, (unsigned)((n_tile + kFixupCols - 1) / kFixupCols));
         cfg.blockDim = dim3(32u * kFixupCols);
@@ -923,11 +850,31 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        // the fix-up kernel's last CTA runs the arrival barrier of a sharded layer
-        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan, sync);
+        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan);
     }
     if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true);
-    return sync.world ? launch_gather_barrier(stream, sync) : cudaSuccess;
+    return cudaSuccess;
+}
+
+cudaError_t launch_gather_barrier(cudaStream_t stream, uint32_t* const* flag_peers, int world, int rank,
+                                  uint32_t* epoch_counter, int* status) {
+    if (!flag_peers || world < 1 || world > kMaxOutTargets || rank < 0 || rank >= world || !epoch_counter || !status)
+        return cudaErrorInvalidValue;
+    PeerFlags flags = {};
+    for (int r = 0; r < world; r++) {
+        if (!flag_peers[r] || (reinterpret_cast<uintptr_t>(flag_peers[r]) & 3)) return cudaErrorInvalidValue;
+        flags.ptr[r] = flag_peers[r];
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_barrier_kernel, flags, world, rank, epoch_counter, status);
 }
 
 }  // namespace fpx

@@ -21,22 +21,16 @@ struct OutTargets {
     uint32_t row0;
 };
 
-// Cross-GPU arrival barrier that ends a sharded layer (needs targets): the launch tells every peer that this rank's
-// stores into its output buffer are complete and waits (bounded) for the same word from every peer.  flag_peers[r] =
-// rank r's flag array (one 32-bit word per rank) as mapped here; epoch_counter = this rank's own call counter in
-// device memory.  Run by the last CTA of the fix-up kernel, or by a one-warp kernel when no fix-up is needed.
-struct PeerArrival {
-    uint32_t* const* flag_peers;
-    uint32_t* epoch_counter;
-    int world;
-    int rank;
-};
-
 // GEMM (+ split-K reduction when split_k > 1).  All pointers are device pointers.  targets == nullptr: the result
 // goes to out[N][M]; otherwise out is ignored (split_k must then be 0 or 1).
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
-                        int* status, const OutTargets* targets = nullptr, const PeerArrival* arrival = nullptr);
+                        int* status, const OutTargets* targets = nullptr);
+// Cross-GPU arrival barrier that ends a sharded layer: tells every peer that this rank's stores into its output
+// buffer are complete and waits (bounded) for the same word from every peer.  flag_peers[r] = rank r's flag array
+// (one 32-bit word per rank) as mapped here; epoch_counter = this rank's own call counter in device memory.
+cudaError_t launch_gather_barrier(cudaStream_t stream, uint32_t* const* flag_peers, int world, int rank,
+                                  uint32_t* epoch_counter, int* status);
 cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k,
                                  bool after_gemm = false);
 int gemm_n_tile(size_t N);
