@@ -251,6 +251,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                         if (!PROF_WAIT(1, ptx::mbar_wait(b_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
                     }
                     PROF_COUNT(6)
+                    if (issued == 0) asm volatile("griddepcontrol.wait;" ::: "memory");   // first read of global memory
                     if (half == 0 && issued == 0) PROF_STAMP(15);
                     PROF_BEGIN(t_issue)
                     const uint32_t bar = full + 8 * pos.idx;
@@ -293,6 +294,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         const uint32_t me = (uint32_t)warp;
         const int q = warp & 3;
         const uint64_t b_desc0 = ptx::smem_desc_k_sw128(ring);
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // before the scales are read and anything is stored
         uint32_t j0 = 0, nseg = 0;
         bool ok = true;
         SegmentIter iter;
@@ -538,6 +540,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__ out, const float* __restrict__ partials,
                                                             size_t elems, int split_k) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialisation
     if (i >= elems) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -570,6 +573,7 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
     const uint32_t r = blockIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a GEMM that follows may set itself up meanwhile
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(10);
     uint32_t first, last;
     plan_tile_owners(plan, r, &first, &last);
@@ -629,6 +633,7 @@ struct PeerFlags {
 constexpr unsigned long long kPeerWaitNs = 2000000000ull;
 __global__ void __launch_bounds__(32) gather_barrier_kernel(const __grid_constant__ PeerFlags flags, int world, int rank,
                                                             uint32_t* epoch_counter, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int r = (int)threadIdx.x;
     const uint32_t epoch = *epoch_counter + 1u;
@@ -696,8 +701,19 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params
         if (err != cudaSuccess) return err;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kernel<<<prm.plan.grid, kThreads, smem, stream>>>(map, prm);
-    return cudaGetLastError();
+    // Programmatic launch: the CTAs may start, set up and find their work while the previous kernel of the stream is
+    // still finishing; every role waits (griddepcontrol.wait) before it first touches global memory.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(prm.plan.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, map, prm);
 }
 
 template <int BW>
