@@ -250,6 +250,10 @@ def run_ours(args):
         mdl["replicas"] = [ShardedFPxLinear(mdl["packed"] if r == 0 else mdl["packed"].clone(), mdl["scale"], mdl["plan"], rank, e, m,
                                             exchange=exchange)
                            for r in range(n_rep)]
+    # The weights are prepacked above and only read from here on: let the GEMMs request them while the previous kernel
+    # of the stream is still finishing (see fp6b200_set_option in include/fp6_llm_b200.h).
+    torch.cuda.synchronize(dev)
+    f.set_static_weights(not args.no_static_weights)
     acts = {(mdl["name"], bs): torch.randn(bs, mdl["ic"], device=dev, dtype=torch.float16) for mdl in models for bs in batches}
     cases = [(mdl, bs) for bs in batches for mdl in models]
     # split_k = 0: the library decomposes the work itself (tile waves + stream-K remainder + fix-up kernel)
@@ -398,7 +402,8 @@ def run_ours(args):
                            f"OC-sharded x{world}, rows stored into every rank's [BS, OC] by the kernel over NVLink + arrival barrier" if exchange is not None
                            else f"OC-sharded x{world} + NCCL all-gather of [BS, OC]"),
                        "l2": f"inputs larger than L2: {replicas} replicas of the layer set ({shard_bytes * replicas / 2**20:.0f} MiB) rotated so a buffer is re-read only after >= 512 MiB of other weights",
-                       "launch": "whole step replayed as a CUDA graph"},
+                       "launch": "whole step replayed as a CUDA graph; kernels launched programmatically (prologue overlaps the previous kernel's tail)",
+                       "static_weights": bool(f.static_weights())},
             "weight_gbs": wbytes_step / sec_step / 1e9,
             "roofline": {"bound": "hbm", "achieved": abytes_step / world / sec_step / 1e9, "peak": hbm_peak, "unit": "GB/s",
                          "frac": abytes_step / world / sec_step / 1e9 / hbm_peak, "traffic": traffic,
@@ -433,6 +438,8 @@ def main():
     ap.add_argument("--split-k", type=int, default=0, help="0 = let the library decompose the work")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused", help="N > 1: how the ranks' rows reach each other")
+    ap.add_argument("--no-static-weights", action="store_true",
+                    help="do not let a GEMM read its (prepacked, read-only) weights before the previous kernel has completed")
     ap.add_argument("--case", default=None, help="LAYER:BATCH - run only this launch shape of the workload (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -104,6 +104,14 @@ int fp6b200_version(void) { return 1; }
 
 const char* fp6b200_error_string(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }
 
+int fp6b200_set_option(int option, int value) {
+    if (option != FP6B200_OPTION_STATIC_WEIGHTS) return cudaErrorInvalidValue;
+    fpx::set_weights_static(value);
+    return cudaSuccess;
+}
+
+int fp6b200_get_option(int option) { return option == FP6B200_OPTION_STATIC_WEIGHTS ? fpx::weights_static() : -1; }
+
 int fp6b200_choose_split_k(size_t M, size_t N, size_t K, int num_sms) { return choose_split_k(M, N, K, num_sms); }
 
 size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k) {

@@ -26,6 +26,7 @@
 // Every mbarrier wait is bounded; on a time-out the CTA records a code in a status word, drains its
 // own copies, frees its tensor memory and returns.
 #include <cuda.h>
+#include <atomic>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -53,7 +54,8 @@ constexpr int kFirstDequantWarp = kProducerWarp + kProducerWarps;
 constexpr int kDequantGroups = 4;        // a group = 4 consecutive warps, one per tensor-memory lane quadrant
 constexpr int kDequantWarps = 4 * kDequantGroups;
 constexpr int kEpilogueWarps = 4;        // = warps 0..3
-constexpr int kWarps = kFirstDequantWarp + kDequantWarps;
+constexpr int kActProducerWarp = kFirstDequantWarp + kDequantWarps;   // the last warp: activation copies (one thread)
+constexpr int kWarps = kActProducerWarp + 1;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kTmemCols = 512;      // the whole tensor memory: one CTA per SM
 
@@ -104,7 +106,7 @@ struct Config {
     static_assert(a_stages >= issuers && stages >= issuers, "rings must be at least as deep as the number of issuers");
     static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
     static_assert(acc_col0 + acc_bufs * issuers * acc_stride <= kTmemCols, "tensor memory budget");
-    static constexpr int num_barriers = 3 * stages + 2 * a_stages + 2 * acc_bufs;
+    static constexpr int num_barriers = 4 * stages + 2 * a_stages + 2 * acc_bufs;
     static constexpr uint32_t smem_bytes = stages * stage_bytes + num_barriers * 8u + 32u;
     static_assert(2u * smem_bytes > 228u * 1024u, "two CTAs must never share an SM: each takes all of tensor memory");
     static_assert(smem_bytes <= 227u * 1024u, "shared memory budget");
@@ -139,6 +141,7 @@ struct Params {
     const uint8_t* region[3];   // start of the 1-bit, 2-bit and 4-bit regions of the packed weights
     const __half* scales;
     OutTargets out;             // where finished fp16 tiles go (this GPU's buffer, or every rank's)
+    uint32_t weights_static;    // the packed weights are not written by earlier work of the stream: read them at once
     float* workspace;
     uint32_t M, N, K;
     WorkPlan plan;
@@ -163,8 +166,9 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     // everything in shared memory is addressed by 32-bit shared-space addresses
     const uint32_t ring = ptx::smem_u32(smem_dyn);
-    const uint32_t full = ring + R * Cfg::stage_bytes;   // barrier arrays, 8 bytes per barrier
-    const uint32_t w_empty = full + 8 * R;               // the unpack warps have read the weights of the stage
+    const uint32_t w_full = ring + R * Cfg::stage_bytes; // barrier arrays, 8 bytes per barrier: the stage's weights have landed
+    const uint32_t b_full = w_full + 8 * R;              // the stage's activations have landed
+    const uint32_t w_empty = b_full + 8 * R;             // the unpack warps have read the weights of the stage
     const uint32_t b_empty = w_empty + 8 * R;            // the MMAs that read the activations of the stage are done
     const uint32_t a_full = b_empty + 8 * R;
     const uint32_t a_empty = a_full + 8 * SA;
@@ -189,7 +193,12 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     // Set-up.  The first producer warp initialises every barrier; the two producer warps then meet on a barrier of
     // their own and start copying at once, while the rest of the CTA waits for the tensor-memory allocation too.
     if (warp == kProducerWarp) {   // one barrier per lane and round
-        for (int i = lane; i < R; i += 32) { ptx::mbar_init(full + 8 * i, kProducerWarps); ptx::mbar_init(w_empty + 8 * i, Cfg::readers); ptx::mbar_init(b_empty + 8 * i, 1); }
+        for (int i = lane; i < R; i += 32) {
+            ptx::mbar_init(w_full + 8 * i, kProducerWarps);
+            ptx::mbar_init(b_full + 8 * i, 1);
+            ptx::mbar_init(w_empty + 8 * i, Cfg::readers);
+            ptx::mbar_init(b_empty + 8 * i, 1);
+        }
         for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, 1); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
         if (lane == 0) *abort_word = 0;
@@ -200,9 +209,10 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTmemCols);
         ptx::tmem_relinquish();
     }
-    if (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) {
+    const bool is_producer = (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) || warp == kActProducerWarp;
+    if (is_producer) {
         __threadfence_block();
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kProducerWarps) : "memory");   // producers: the barriers exist
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * (kProducerWarps + 1)) : "memory");   // producers: the barriers exist
         asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");            // tell the others, do not wait
     } else {
         ptx::tc_fence_before_sync();
@@ -212,18 +222,23 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     if (threadIdx.x == 0) PROF_STAMP(1);
     const uint32_t tmem_base = *tmem_holder;   // valid for every warp but the producers, which never use it
 
-    if (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) {
-        // ------------------------------------------------------------ producers: warp 4 copies the activations and the
-        // weight segments of the tile's first 64-row block, warp 5 those of the second (one thread each)
+    if (is_producer) {
+        // ------------------------------------------------------------ producers (one thread each): warps 4 and 5 copy the
+        // weight segments of the tile's first / second 64-row block, the last warp the activations (one 3-D TMA box per
+        // stage).  Weights declared static are requested before griddepcontrol.wait, i.e. while the previous kernel
+        // of the stream may still be running; everything else waits for it.
         if (lane == 0) {
-            const uint32_t half = (uint32_t)(warp - kProducerWarp);
-            if (half == 0) PROF_STAMP(13);
-            const uint64_t pol_w = ptx::policy_evict_first();
-            const uint64_t pol_b = ptx::policy_evict_last();
+            const bool acts = warp == kActProducerWarp;
+            const uint32_t half = acts ? 0u : (uint32_t)(warp - kProducerWarp);
+            if (warp == kProducerWarp) PROF_STAMP(13);
+            const uint64_t pol = acts ? ptx::policy_evict_last() : ptx::policy_evict_first();
             const uint64_t kblocks = plan.kblocks;
             const uint8_t* reg1 = p.region[0];
             const uint8_t* reg2 = p.region[1];
             const uint8_t* reg4 = p.region[2];
+            const uint32_t my_full = acts ? b_full : w_full;
+            const uint32_t my_empty = kUnified ? a_empty : (acts ? b_empty : w_empty);
+            bool waited = !acts && p.weights_static != 0;   // nothing to wait for before static weights are read
             ptx::RingPos<R> pos;
             pos.set(0);
             uint32_t issued = 0;
@@ -238,42 +253,35 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 const int32_t n0 = (int32_t)((seg.tile - m_tile * plan.n_tiles) * N_TILE);
                 const uint32_t nstages = (seg.nkb + KS - 1) / KS;
                 uint32_t sidx = plan_first_stage(cta, nstages);   // stage of the segment's K range handled next
-                if (half == 0 && issued == 0) PROF_STAMP(14);
+                if (warp == kProducerWarp && issued == 0) PROF_STAMP(14);
                 for (uint32_t i = 0; i < nstages; i++) {
                     const uint32_t kb_off = sidx * KS;
                     const uint32_t cnt = seg.nkb - kb_off < (uint32_t)KS ? seg.nkb - kb_off : (uint32_t)KS;
                     sidx = sidx + 1 == nstages ? 0u : sidx + 1;
-                    const uint32_t par = pos.lap ^ 1u;
-                    if (kUnified) {
-                        if (!PROF_WAIT(0, ptx::mbar_wait(a_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
-                    } else {
-                        if (!PROF_WAIT(0, ptx::mbar_wait(w_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
-                        if (!PROF_WAIT(1, ptx::mbar_wait(b_empty + 8 * pos.idx, par, abort_word, kErrStageEmpty))) { ok = false; break; }
-                    }
+                    if (!PROF_WAIT(0, ptx::mbar_wait(my_empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty))) { ok = false; break; }
                     PROF_COUNT(6)
-                    if (issued == 0) asm volatile("griddepcontrol.wait;" ::: "memory");   // first read of global memory
-                    if (half == 0 && issued == 0) PROF_STAMP(15);
+                    if (!waited) {
+                        asm volatile("griddepcontrol.wait;" ::: "memory");   // first read of memory the previous kernel may write
+                        waited = true;
+                    }
+                    if (warp == kProducerWarp && issued == 0) PROF_STAMP(15);
                     PROF_BEGIN(t_issue)
-                    const uint32_t bar = full + 8 * pos.idx;
+                    const uint32_t bar = my_full + 8 * pos.idx;
                     const uint32_t dst = ring + pos.idx * Cfg::stage_bytes;
-                    // the activation copy always brings KS blocks (blocks past K are zero-filled), the weight copies cnt
-                    if (half == 0) {
-#if defined(FPX_EXP) && (FPX_EXP & 8)
-                        ptx::mbar_arrive_expect_tx(bar, cnt * (Raw::bytes128 / 2));
-#else
-                        ptx::mbar_arrive_expect_tx(bar, KS * Cfg::b_block + cnt * (Raw::bytes128 / 2));
-                        ptx::tma_load_3d(dst, &act_map, 0, n0, (int32_t)(seg.kb_begin + kb_off), bar, pol_b);
-#endif
+                    if (acts) {
+                        // always KS blocks: blocks past the end of K are zero-filled by the copy
+                        ptx::mbar_arrive_expect_tx(bar, KS * Cfg::b_block);
+                        ptx::tma_load_3d(dst, &act_map, 0, n0, (int32_t)(seg.kb_begin + kb_off), bar, pol);
                     } else {
                         ptx::mbar_arrive_expect_tx(bar, cnt * (Raw::bytes128 / 2));
+                        const uint64_t b0 = blk0 + kb_off;
+                        if (Raw::seg1) ptx::bulk_g2s(dst + Cfg::off1 + half * KS * Raw::seg1, reg1 + b0 * Raw::seg1, cnt * Raw::seg1, bar, pol);
+                        if (Raw::seg2) ptx::bulk_g2s(dst + Cfg::off2 + half * KS * Raw::seg2, reg2 + b0 * Raw::seg2, cnt * Raw::seg2, bar, pol);
+                        if (Raw::seg4) ptx::bulk_g2s(dst + Cfg::off4 + half * KS * Raw::seg4, reg4 + b0 * Raw::seg4, cnt * Raw::seg4, bar, pol);
                     }
-                    const uint64_t b0 = blk0 + kb_off;
-                    if (Raw::seg1) ptx::bulk_g2s(dst + Cfg::off1 + half * KS * Raw::seg1, reg1 + b0 * Raw::seg1, cnt * Raw::seg1, bar, pol_w);
-                    if (Raw::seg2) ptx::bulk_g2s(dst + Cfg::off2 + half * KS * Raw::seg2, reg2 + b0 * Raw::seg2, cnt * Raw::seg2, bar, pol_w);
-                    if (Raw::seg4) ptx::bulk_g2s(dst + Cfg::off4 + half * KS * Raw::seg4, reg4 + b0 * Raw::seg4, cnt * Raw::seg4, bar, pol_w);
                     PROF_END(3, t_issue)
                     pos.advance(1);
-                    if (half == 0) { if (issued == 0) PROF_STAMP(2); PROF_STAMP(3); }
+                    if (warp == kProducerWarp) { if (issued == 0) PROF_STAMP(2); PROF_STAMP(3); }
                     issued++;
                 }
             }
@@ -281,7 +289,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
                 const uint32_t first = issued > (uint32_t)R ? issued - R : 0u;
                 for (uint32_t t = first; t < issued; t++)
-                    ptx::mbar_wait(full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, 64, 50000000ull);
+                    ptx::mbar_wait(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, 64, 50000000ull);
             }
         }
         __syncwarp();
@@ -320,7 +328,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull))) { ok = false; break; }
                     if (me == 0 && nseg == 0 && t == me) PROF_STAMP(5);
                     // the activations of the stage landed before its weights were unpacked; this only makes them visible here
-                    if (!PROF_WAIT(1, ptx::mbar_wait(full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                    if (!PROF_WAIT(1, ptx::mbar_wait(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
                     PROF_BEGIN(t_issue)
                     ptx::tc_fence_after_sync();
@@ -415,7 +423,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             nseg++;
         }
         PROF_FLUSH();
-    } else if (warp >= kFirstDequantWarp) {
+    } else if (warp >= kFirstDequantWarp && warp < kActProducerWarp) {
         // ------------------------------------------------------------ unpack warps
         const int q = warp & 3;                                   // tensor-memory lane quadrant this warp may touch
         const uint32_t group = (uint32_t)(warp - kFirstDequantWarp) >> 2;
@@ -448,7 +456,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 while (sidx >= nstages) sidx -= nstages;
                 const bool valid = sidx * KS + kbi < seg.nkb;    // the last stage of the K range may hold fewer K blocks
                 sidx += kStageGroups;
-                if (!PROF_WAIT(0, ptx::mbar_wait(full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                if (!PROF_WAIT(0, ptx::mbar_wait(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                 if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == turn) PROF_STAMP(4);
                 PROF_COUNT(6)
                 PROF_BEGIN(t_math)
@@ -773,6 +781,10 @@ cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* 
     return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, out, partials, elems, split_k);
 }
 
+static std::atomic<int> g_weights_static{0};
+void set_weights_static(int on) { g_weights_static.store(on ? 1 : 0); }
+int weights_static() { return g_weights_static.load(); }
+
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
                         int* status, const OutTargets* targets) {
@@ -819,6 +831,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     prm.scales = scales;
     prm.out = where;
     prm.workspace = workspace;
+    prm.weights_static = (uint32_t)weights_static();
     prm.M = (uint32_t)M;
     prm.N = (uint32_t)N;
     prm.K = (uint32_t)K;

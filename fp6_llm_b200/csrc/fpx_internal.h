@@ -33,6 +33,10 @@ cudaError_t launch_gather_barrier(cudaStream_t stream, uint32_t* const* flag_pee
                                   uint32_t* epoch_counter, int* status);
 cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k,
                                  bool after_gemm = false);
+// Process-wide promise that packed weights are never written by work still in flight on the stream of a GEMM that
+// reads them; the GEMM then requests them before the previous kernel of its stream has completed.  Off by default.
+void set_weights_static(int on);
+int weights_static();
 int gemm_n_tile(size_t N);
 int device_sm_count();
 // Workspace the GEMM needs when it picks its own decomposition (split_k == 0).

@@ -229,6 +229,18 @@ def linear_forward_host(EXPONENT: int, MANTISSA: int, act_host: torch.Tensor, pa
     return out_host
 
 
+def set_static_weights(on: bool) -> None:
+    """Promise (or withdraw the promise) that packed weights are prepacked ahead of time and only read afterwards:
+    no work still in flight on a stream writes the weights of a linear layer launched on that stream.  The GEMM then
+    requests and unpacks its first weight stages while the previous kernel of the stream is still finishing.
+    After a prepack, synchronise (or wait on an event) before the first layer that uses the result."""
+    _native.check(_native.lib().fp6b200_set_option(1, 1 if on else 0), "fp6b200_set_option")
+
+
+def static_weights() -> bool:
+    return _native.lib().fp6b200_get_option(1) == 1
+
+
 def device_status() -> int:
     """Synchronise and return (then clear) the time-out code a GEMM CTA may have recorded; 0 = healthy."""
     code = ctypes.c_int(0)

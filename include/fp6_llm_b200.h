@@ -136,6 +136,21 @@ int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weig
                           int split_k);
 
 /*
+ * Process-wide options (no counterpart in the reference).
+ * FP6B200_OPTION_STATIC_WEIGHTS (default 0): set to 1 to promise that no packed-weight buffer handed to fp6b200_linear*
+ * is written by work that is still in flight on the same stream when the call is made (weights prepacked at load time
+ * and then only read).  The GEMM is launched programmatically: its CTAs start while the previous kernel of the stream
+ * is finishing, and with this option they already request the first weight stages and unpack them then; activations,
+ * scales, outputs and workspace are touched only after the previous kernel has completed, option or not.
+ * With the option on, a prepack (or any write of the weights) must be followed by a synchronisation or an event wait
+ * before the first GEMM that reads them.  fp6b200_set_option returns cudaErrorInvalidValue for an unknown option;
+ * fp6b200_get_option returns the value, or -1.
+ */
+#define FP6B200_OPTION_STATIC_WEIGHTS 1
+int fp6b200_set_option(int option, int value);
+int fp6b200_get_option(int option);
+
+/*
  * Synchronises the current device, returns in *code the first time-out code a GEMM CTA recorded
  * since the last call (0 = none) and clears it.  A non-zero code means a bounded wait inside the
  * kernel gave up and the output of that launch is invalid.

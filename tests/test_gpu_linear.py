@@ -155,3 +155,29 @@ def test_error_behaviour(oracle_mod, native_lib):
     assert native_lib.fp6b200_linear(3, 2, None, packed.data_ptr(), s.data_ptr(), x.data_ptr(), out.data_ptr(), 256, 0, 256, None, 1) == bad
     assert native_lib.fp6b200_linear(3, 2, None, packed.data_ptr(), s.data_ptr(), x.data_ptr(), out.data_ptr(), 256, 4, 256, None, 2) == bad
     assert native_lib.fp6b200_linear(1, 2, None, packed.data_ptr(), s.data_ptr(), x.data_ptr(), out.data_ptr(), 256, 4, 256, None, 1) == bad
+
+
+def test_static_weights_option_gives_identical_results(native_lib):
+    """With the static-weights promise the GEMM requests its weights while the previous kernel of the stream is still
+    finishing; the weights here are prepacked and synchronised first, so the results must not change by a bit."""
+    import fp6_llm_b200 as f
+    from fp6_llm_b200.formats import random_codes_layer
+    layers = []
+    for i, (oc, ic) in enumerate(((4096, 4096), (1536, 2048), (512, 11008))):
+        w, s = random_codes_layer(oc, ic, 3, 2, seed=20 + i, scale_lo=0.01, scale_hi=0.1)
+        layers.append((f.weight_prepacking_cpu(w.cuda()), s.cuda(), torch.randn(8 + 24 * i, ic, generator=torch.Generator().manual_seed(i)).half().cuda()))
+    torch.cuda.synchronize()
+    assert not f.static_weights()
+    plain = [f.linear_forward_cuda(x, p, s, 0) for p, s, x in layers]
+    try:
+        f.set_static_weights(True)
+        assert f.static_weights()
+        for _ in range(3):                                   # back to back on one stream: each GEMM follows a fix-up kernel
+            fast = [f.linear_forward_cuda(x, p, s, 0) for p, s, x in layers]
+            assert f.device_status() == 0
+            for a, b in zip(plain, fast):
+                assert torch.equal(a, b)
+    finally:
+        f.set_static_weights(False)
+    assert native_lib.fp6b200_set_option(99, 1) == 1         # unknown option: cudaErrorInvalidValue
+    assert native_lib.fp6b200_get_option(99) == -1
