@@ -88,7 +88,9 @@ struct Config {
     static constexpr bool unified = a_stages == stages;
     // One thread can issue an MMA only every ~60-90 cycles, far more than a narrow MMA needs on the tensor
     // pipe, so narrow tiles are issued by several warps, each into its own accumulator (summed in the epilogue).
-    static constexpr int issuers = N_TILE <= 32 ? (ks == 4 ? 2 : 4) : (N_TILE <= 128 ? 2 : 1);
+    // issuing warps: every one visits every stage and takes the K blocks me, me + issuers, ... of it (so a stage's MMAs
+    // are issued in 1/issuers of the time one thread would need, and its ring slots come back that much sooner)
+    static constexpr int issuers = ks < 4 ? ks : 4;
     static constexpr int acc_bufs = 1;   // the issuing warps also run the epilogue, so one set of accumulators suffices
     static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
     static constexpr uint32_t w_off = ks * b_block;
@@ -103,7 +105,7 @@ struct Config {
     // An issuer waits on a ring slot only every `issuers` stages.  A parity wait is only meaningful when the
     // slot's previous phase is already complete, which the issuer knows from its own previous wait as long as
     // the rings are at least `issuers` deep.
-    static_assert(a_stages >= issuers && stages >= issuers, "rings must be at least as deep as the number of issuers");
+    static_assert(issuers <= kMaxIssuers && ks % issuers == 0, "K blocks of a stage are dealt out evenly to the issuers");
     static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
     static_assert(acc_col0 + acc_bufs * issuers * acc_stride <= kTmemCols, "tensor memory budget");
     static constexpr int num_barriers = 4 * stages + 2 * a_stages + 2 * acc_bufs;
@@ -197,9 +199,9 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             ptx::mbar_init(w_full + 8 * i, kProducerWarps);
             ptx::mbar_init(b_full + 8 * i, 1);
             ptx::mbar_init(w_empty + 8 * i, Cfg::readers);
-            ptx::mbar_init(b_empty + 8 * i, 1);
+            ptx::mbar_init(b_empty + 8 * i, NI);
         }
-        for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, 1); }
+        for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, NI); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
         if (lane == 0) *abort_word = 0;
         ptx::fence_barrier_init();
@@ -295,8 +297,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         __syncwarp();
     } else if (warp < kMaxIssuers) {
         // ------------------------------------------------------------ MMA issue + epilogue
-        // Per segment: lane 0 of the first NI warps issues the MMAs (issuer i takes the stages t = i mod NI and
-        // accumulates them in its own accumulator); then all four warps, one per tensor-memory lane quadrant,
+        // Per segment: lane 0 of the first NI warps issues the MMAs (issuer i takes the K blocks i, i + NI, ... of every
+        // stage and accumulates them in its own accumulator); then all four warps, one per tensor-memory lane quadrant,
         // read the accumulators, add them and store the tile (lane = output channel, column = token).
         constexpr uint32_t idesc = ptx::idesc_f16_f32(kTileM, N_TILE);
         const uint32_t me = (uint32_t)warp;
@@ -317,16 +319,15 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 const uint32_t d_tmem = tmem_base + Cfg::acc_col0 + me * Cfg::acc_stride;
                 ptx::RingPos<R> rp;
                 ptx::RingPos<SA> ap;
-                rp.set(j0 + me);
-                ap.set(j0 + me);
-                uint32_t sidx = plan_first_stage(cta, nstages) + me;          // stage of the segment's K range handled next
-                uint32_t accumulate = 0u;                                    // 0 only for the first MMA of the segment
-                for (uint32_t t = me; ok && t < nstages; t += NI) {
-                    while (sidx >= nstages) sidx -= nstages;
+                rp.set(j0);
+                ap.set(j0);
+                uint32_t sidx = plan_first_stage(cta, nstages);               // stage of the segment's K range handled next
+                uint32_t accumulate = 0u;                                    // 0 only for this issuer's first MMA of the segment
+                for (uint32_t t = 0; ok && t < nstages; t++) {
                     const uint32_t cnt = seg.nkb - sidx * KS < (uint32_t)KS ? seg.nkb - sidx * KS : (uint32_t)KS;
-                    sidx += NI;
+                    sidx = sidx + 1 == nstages ? 0u : sidx + 1;
                     if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull))) { ok = false; break; }
-                    if (me == 0 && nseg == 0 && t == me) PROF_STAMP(5);
+                    if (me == 0 && nseg == 0 && t == 0) PROF_STAMP(5);
                     // the activations of the stage landed before its weights were unpacked; this only makes them visible here
                     if (!PROF_WAIT(1, ptx::mbar_wait(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
@@ -336,7 +337,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     const uint32_t a_tmem = tmem_base + ap.idx * Cfg::a_cols;
 #if !(defined(FPX_EXP) && (FPX_EXP & 4))
 #pragma unroll
-                    for (uint32_t kbi = 0; kbi < (uint32_t)KS; kbi++)
+                    for (uint32_t kbi = me; kbi < (uint32_t)KS; kbi += NI)   // (me is warp-uniform; the loop has KS / NI rounds)
                         if (kbi < cnt) {
 #pragma unroll
                             for (uint32_t kk = 0; kk < 4; kk++) {   // four K=16 steps; B advances 32 bytes inside the swizzle row
@@ -352,13 +353,10 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     if (!kUnified) ptx::tc_commit(b_empty + 8 * rp.idx);
                     PROF_END(4, t_commit)
                     if (me == 0) PROF_STAMP(6);
-                    rp.advance(NI);
-                    ap.advance(NI);
+                    rp.advance(1);
+                    ap.advance(1);
                 }
-                if (ok) {
-                    if (me < nstages) ptx::tc_commit(acc_full);   // arrives once this issuer's MMAs are done
-                    else ptx::mbar_arrive(acc_full);              // nothing to add to this segment
-                }
+                if (ok) ptx::tc_commit(acc_full);   // arrives once this issuer's MMAs (if any) are done
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
@@ -373,7 +371,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             if (threadIdx.x == 0) PROF_STAMP(7);
             ptx::tc_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::acc_col0;
-            const uint32_t parts = nstages < (uint32_t)NI ? nstages : (uint32_t)NI;   // issuers that contributed
+            // issuers that contributed: the fullest stage of the segment holds min(KS, nkb) K blocks
+            const uint32_t parts = seg.nkb < (uint32_t)NI ? seg.nkb : (uint32_t)NI;
             constexpr int CH = 16;   // columns handled per round
 #pragma unroll 1
             for (int c0 = 0; c0 < N_TILE; c0 += CH) {
@@ -548,7 +547,6 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__ out, const float* __restrict__ partials,
                                                             size_t elems, int split_k) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialisation
     if (i >= elems) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -576,16 +574,20 @@ constexpr int kFixupCols = 16;
 constexpr uint64_t kEvenGridMinPercent = FPX_EVEN_PCT;
 constexpr uint64_t kMinUnitsPerCta = 8;   // a CTA is not started for fewer 64-K blocks than this (two 256-K stages)
 __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
-                                                                         uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan) {
+                                                                         uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan,
+                                                                         int early_trigger) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
     const uint32_t r = blockIdx.x;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a GEMM that follows may set itself up meanwhile
+    if (early_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a GEMM that follows may set itself up meanwhile
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(10);
     uint32_t first, last;
     plan_tile_owners(plan, r, &first, &last);
-    if (first == last) return;
+    if (first == last) {   // one CTA computed the whole tile and stored it; still do not finish before the GEMM has
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        return;
+    }
     const uint32_t tile = plan_full_waves(plan) * plan.grid + r;
     const uint32_t m_tile = tile / plan.n_tiles, n_tile = tile % plan.n_tiles;
     const uint32_t span = last - first + 1 < kMaxGrid ? last - first + 1 : kMaxGrid;
@@ -716,9 +718,11 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
+    // Not for the 256-wide tile: chains of such launches on a large layer (8192 x 28672, batch 1024) ended in a launch
+    // failure whose cause has not been found; that configuration keeps plain stream order between launches.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[0].val.programmaticStreamSerializationAllowed = N_TILE <= 128 ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, map, prm);
@@ -879,7 +883,8 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan);
+        const int early = n_tile <= 128 ? 1 : 0;   // wide tiles: plain stream order all the way (see launch_one)
+        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan, early);
     }
     if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true);
     return cudaSuccess;
