@@ -88,9 +88,12 @@ struct Config {
     static constexpr bool unified = a_stages == stages;
     // One thread can issue an MMA only every ~60-90 cycles, far more than a narrow MMA needs on the tensor
     // pipe, so narrow tiles are issued by several warps, each into its own accumulator (summed in the epilogue).
-    // issuing warps: every one visits every stage and takes the K blocks me, me + issuers, ... of it (so a stage's MMAs
-    // are issued in 1/issuers of the time one thread would need, and its ring slots come back that much sooner)
-    static constexpr int issuers = ks < 4 ? ks : 4;
+    // Issuing warps.  Narrow tiles (256-K stages): every issuer visits every stage and takes the K blocks me, me + 4,
+    // ... of it, so a stage's 16 MMAs are issued in a quarter of the time one thread would need and its ring slots come
+    // back that much sooner.  Wider tiles: issuer i takes the stages i, i + issuers, ... whole (measured faster there).
+    static constexpr bool split_stage = ks == 4;
+    static constexpr int issuers = split_stage ? 4 : (N_TILE <= 128 ? 2 : 1);
+    static constexpr int slot_commits = split_stage ? issuers : 1;   // commits that free a ring slot
     static constexpr int acc_bufs = 1;   // the issuing warps also run the epilogue, so one set of accumulators suffices
     static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
     static constexpr uint32_t w_off = ks * b_block;
@@ -105,7 +108,9 @@ struct Config {
     // An issuer waits on a ring slot only every `issuers` stages.  A parity wait is only meaningful when the
     // slot's previous phase is already complete, which the issuer knows from its own previous wait as long as
     // the rings are at least `issuers` deep.
-    static_assert(issuers <= kMaxIssuers && ks % issuers == 0, "K blocks of a stage are dealt out evenly to the issuers");
+    static_assert(issuers <= kMaxIssuers, "issuing warps are the first warps of the CTA");
+    static_assert(split_stage ? ks % issuers == 0 : (a_stages >= issuers && stages >= issuers),
+                  "K blocks dealt out evenly, or rings at least as deep as the number of issuers that stride over them");
     static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
     static_assert(acc_col0 + acc_bufs * issuers * acc_stride <= kTmemCols, "tensor memory budget");
     static constexpr int num_barriers = 4 * stages + 2 * a_stages + 2 * acc_bufs;
@@ -199,9 +204,9 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             ptx::mbar_init(w_full + 8 * i, kProducerWarps);
             ptx::mbar_init(b_full + 8 * i, 1);
             ptx::mbar_init(w_empty + 8 * i, Cfg::readers);
-            ptx::mbar_init(b_empty + 8 * i, NI);
+            ptx::mbar_init(b_empty + 8 * i, Cfg::slot_commits);
         }
-        for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, NI); }
+        for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, Cfg::slot_commits); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
         if (lane == 0) *abort_word = 0;
         ptx::fence_barrier_init();
@@ -319,15 +324,18 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 const uint32_t d_tmem = tmem_base + Cfg::acc_col0 + me * Cfg::acc_stride;
                 ptx::RingPos<R> rp;
                 ptx::RingPos<SA> ap;
-                rp.set(j0);
-                ap.set(j0);
-                uint32_t sidx = plan_first_stage(cta, nstages);               // stage of the segment's K range handled next
+                constexpr uint32_t kStep = Cfg::split_stage ? 1u : (uint32_t)NI;   // stages between two visits of this issuer
+                const uint32_t t0 = Cfg::split_stage ? 0u : me;
+                rp.set(j0 + t0);
+                ap.set(j0 + t0);
+                uint32_t sidx = plan_first_stage(cta, nstages) + t0;          // stage of the segment's K range handled next
                 uint32_t accumulate = 0u;                                    // 0 only for this issuer's first MMA of the segment
-                for (uint32_t t = 0; ok && t < nstages; t++) {
+                for (uint32_t t = t0; ok && t < nstages; t += kStep) {
+                    while (sidx >= nstages) sidx -= nstages;
                     const uint32_t cnt = seg.nkb - sidx * KS < (uint32_t)KS ? seg.nkb - sidx * KS : (uint32_t)KS;
-                    sidx = sidx + 1 == nstages ? 0u : sidx + 1;
+                    sidx += kStep;
                     if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull))) { ok = false; break; }
-                    if (me == 0 && nseg == 0 && t == 0) PROF_STAMP(5);
+                    if (me == 0 && nseg == 0 && t == t0) PROF_STAMP(5);
                     // the activations of the stage landed before its weights were unpacked; this only makes them visible here
                     if (!PROF_WAIT(1, ptx::mbar_wait(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
@@ -337,7 +345,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     const uint32_t a_tmem = tmem_base + ap.idx * Cfg::a_cols;
 #if !(defined(FPX_EXP) && (FPX_EXP & 4))
 #pragma unroll
-                    for (uint32_t kbi = me; kbi < (uint32_t)KS; kbi += NI)   // (me is warp-uniform; the loop has KS / NI rounds)
+                    for (uint32_t kbi = Cfg::split_stage ? me : 0u; kbi < (uint32_t)KS; kbi += Cfg::split_stage ? (uint32_t)NI : 1u)
                         if (kbi < cnt) {
 #pragma unroll
                             for (uint32_t kk = 0; kk < 4; kk++) {   // four K=16 steps; B advances 32 bytes inside the swizzle row
@@ -353,8 +361,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     if (!kUnified) ptx::tc_commit(b_empty + 8 * rp.idx);
                     PROF_END(4, t_commit)
                     if (me == 0) PROF_STAMP(6);
-                    rp.advance(1);
-                    ap.advance(1);
+                    rp.advance(kStep);
+                    ap.advance(kStep);
                 }
                 if (ok) ptx::tc_commit(acc_full);   // arrives once this issuer's MMAs (if any) are done
             }
@@ -371,8 +379,10 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             if (threadIdx.x == 0) PROF_STAMP(7);
             ptx::tc_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::acc_col0;
-            // issuers that contributed: the fullest stage of the segment holds min(KS, nkb) K blocks
-            const uint32_t parts = seg.nkb < (uint32_t)NI ? seg.nkb : (uint32_t)NI;
+            // issuers that contributed: the fullest stage of the segment holds min(KS, nkb) K blocks (dealt to the issuers),
+            // or, when the issuers take whole stages, one issuer per stage
+            const uint32_t have = Cfg::split_stage ? seg.nkb : nstages;
+            const uint32_t parts = have < (uint32_t)NI ? have : (uint32_t)NI;
             constexpr int CH = 16;   // columns handled per round
 #pragma unroll 1
             for (int c0 = 0; c0 < N_TILE; c0 += CH) {
