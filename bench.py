@@ -39,7 +39,7 @@ WORKLOADS = {
                        [1, 16, 64]),
     "llama2-70b-fp6": (3, 2, [("qkv", 10240, 8192), ("o", 8192, 8192), ("gate_up", 57344, 8192), ("down", 8192, 28672)],
                        [1, 4, 16, 64, 128]),
-    "llama2-70b-prefill-fp6": (3, 2, [("gate_up", 57344, 8192), ("down", 8192, 28672)], [512, 1024, 2048]),
+    "llama2-70b-prefill-fp6": (3, 2, [("gate_up", 57344, 8192)], [512, 1024, 2048]),
     "single-4096-fp6": (3, 2, [("square", 4096, 4096)], [8]),
 }
 DEFAULT_WORKLOAD = "llama2-7b-fp6"
