@@ -104,7 +104,14 @@ struct Config {
     static constexpr uint32_t a_cols = ks * kAColsPerKBlock;
     static constexpr uint32_t acc_col0 = a_stages * a_cols;
     static constexpr uint32_t acc_stride = N_TILE < 32 ? 32u : (uint32_t)N_TILE;
-    static constexpr int readers = 4 * ks;   // unpack warps per stage
+    // Unpack warps: kDequantGroups groups of four warps (one per tensor-memory lane quadrant) form `teams` teams that
+    // take turns on consecutive stages; inside a team every group unpacks kb_per_warp K blocks of the stage.  Two teams
+    // at least, so that one team computes while the other waits for data or a free slot and stores.
+    static constexpr int teams = ks == 1 ? 4 : 2;
+    static constexpr int groups_per_team = kDequantGroups / teams;
+    static constexpr int kb_per_warp = ks / groups_per_team;
+    static_assert(kDequantGroups % teams == 0 && ks % groups_per_team == 0 && kb_per_warp >= 1, "unpack work split");
+    static constexpr int readers = 4 * groups_per_team;   // unpack warps per stage
     // An issuer waits on a ring slot only every `issuers` stages.  A parity wait is only meaningful when the
     // slot's previous phase is already complete, which the issuer knows from its own previous wait as long as
     // the rings are at least `issuers` deep.
@@ -436,16 +443,17 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         // ------------------------------------------------------------ unpack warps
         const int q = warp & 3;                                   // tensor-memory lane quadrant this warp may touch
         const uint32_t group = (uint32_t)(warp - kFirstDequantWarp) >> 2;
-        constexpr uint32_t kStageGroups = kDequantGroups / KS;   // groups that take turns on consecutive stages
-        const uint32_t kbi = group % KS;                         // K block of the stage this warp unpacks
-        const uint32_t turn = group / KS;                        // it takes the stages j with j % kStageGroups == turn
+        constexpr uint32_t kStageGroups = Cfg::teams;             // teams take turns on consecutive stages
+        constexpr int KPW = Cfg::kb_per_warp;                     // K blocks of a stage this warp unpacks
+        const uint32_t turn = group % kStageGroups;               // it takes the stages j with j % kStageGroups == turn
+        const uint32_t kb0 = (group / kStageGroups) * KPW;        // its first K block inside a stage
         const int h = q & 1;                                      // sub-blocks 2h, 2h+1 of the 64-row block
         const int rb = q >> 1;                                    // 64-row block inside the 128-row tile
         const uint32_t lane_base = ring + 4u * lane;
-        const uint32_t o4 = Cfg::off4 + (rb * KS + kbi) * Raw::seg4 + 2 * h * 128;
-        const uint32_t o2 = Cfg::off2 + (rb * KS + kbi) * Raw::seg2 + h * 128;
-        const uint32_t o1 = Cfg::off1 + (rb * KS + kbi) * Raw::seg1;
-        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * q) << 16) + kbi * kAColsPerKBlock;
+        const uint32_t o4 = Cfg::off4 + (rb * KS + kb0) * Raw::seg4 + 2 * h * 128;
+        const uint32_t o2 = Cfg::off2 + (rb * KS + kb0) * Raw::seg2 + h * 128;
+        const uint32_t o1 = Cfg::off1 + (rb * KS + kb0) * Raw::seg1;
+        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * q) << 16) + kb0 * kAColsPerKBlock;
         uint32_t j0 = 0;   // running stage index at the start of the segment
         bool ok = true;
         SegmentIter iter;
@@ -463,37 +471,33 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             uint32_t sidx = plan_first_stage(cta, nstages) + t;   // stage of the segment's K range handled next
             for (; t < nstages; t += kStageGroups) {
                 while (sidx >= nstages) sidx -= nstages;
-                const bool valid = sidx * KS + kbi < seg.nkb;    // the last stage of the K range may hold fewer K blocks
+                // K blocks of this stage that exist for this warp (the last stage of the K range may hold fewer)
+                const uint32_t in_stage = seg.nkb - sidx * KS;
+                const uint32_t mine = in_stage > kb0 ? (in_stage - kb0 < (uint32_t)KPW ? in_stage - kb0 : (uint32_t)KPW) : 0u;
                 sidx += kStageGroups;
                 if (!PROF_WAIT(0, ptx::mbar_wait(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                 if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == turn) PROF_STAMP(4);
                 PROF_COUNT(6)
-                PROF_BEGIN(t_math)
-                uint32_t v[2][16];
-                if (valid) {
-                    const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
+                const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
+                const uint32_t a_addr = a_lane + ap.idx * Cfg::a_cols;
+                bool slot_free = false;
+#pragma unroll
+                for (int b = 0; b < KPW; b++) {
+                    if ((uint32_t)b >= mine) break;
+                    PROF_BEGIN(t_math)
+                    uint32_t v[2][16];
                     uint32_t w4[4][2], w2[4], w1[4];
 #pragma unroll
                     for (int jj = 0; jj < 4; jj++) {
-#if defined(FPX_EXP) && (FPX_EXP & 32)
-                        w4[jj][0] = raw + jj; w4[jj][1] = raw - jj; w2[jj] = raw * 3; w1[jj] = raw * 5;
-                        continue;
-#endif
-                        w4[jj][0] = ptx::lds_u32(raw + o4 + (jj * 4 + 0) * 128);
-                        w4[jj][1] = ptx::lds_u32(raw + o4 + (jj * 4 + 1) * 128);
-                        w2[jj] = Raw::seg2 ? ptx::lds_u32(raw + o2 + (jj * 2) * 128) : 0u;
-                        w1[jj] = Raw::seg1 ? ptx::lds_u32(raw + o1 + jj * 128) : 0u;
+                        w4[jj][0] = ptx::lds_u32(raw + o4 + b * Raw::seg4 + (jj * 4 + 0) * 128);
+                        w4[jj][1] = ptx::lds_u32(raw + o4 + b * Raw::seg4 + (jj * 4 + 1) * 128);
+                        w2[jj] = Raw::seg2 ? ptx::lds_u32(raw + o2 + b * Raw::seg2 + (jj * 2) * 128) : 0u;
+                        w1[jj] = Raw::seg1 ? ptx::lds_u32(raw + o1 + b * Raw::seg1 + jj * 128) : 0u;
                     }
-                    if (!kUnified) {
+                    if (!kUnified && (uint32_t)b + 1 == mine) {
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);   // the weights can be refilled while we compute
                     }
-#if defined(FPX_EXP) && (FPX_EXP & 1)
-#pragma unroll
-                    for (int jj = 0; jj < 4; jj++)
-#pragma unroll
-                        for (int i = 0; i < 4; i++) { v[0][4 * jj + i] = w4[jj][0] + i + w2[jj]; v[1][4 * jj + i] = w4[jj][1] + i + w1[jj]; }
-#else
 #pragma unroll
                     for (int jj = 0; jj < 4; jj++) {
                         uint32_t pat[8];
@@ -501,27 +505,24 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
 #pragma unroll
                         for (int kk = 0; kk < 2; kk++)
 #pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                v[kk][4 * jj + i] = pat[4 * kk + i];
-                            }
+                            for (int i = 0; i < 4; i++) v[kk][4 * jj + i] = pat[4 * kk + i];
                     }
-#endif
-                } else if (!kUnified) {
-                    if (lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);
+                    PROF_END(1, t_math)
+                    if (!slot_free) {
+                        if (!PROF_WAIT(2, ptx::mbar_wait(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                        slot_free = true;
+                    }
+                    ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock, v[0]);
+                    ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock + (16u << 16), v[1]);
                 }
-                PROF_END(1, t_math)
-                if (!PROF_WAIT(2, ptx::mbar_wait(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                if (!ok) break;
                 PROF_BEGIN(t_st)
-                if (valid) {
-                    ptx::tc_fence_after_sync();
-                    const uint32_t a_addr = a_lane + ap.idx * Cfg::a_cols;
-#if defined(FPX_EXP) && (FPX_EXP & 2)
-                    if (v[0][0] == 0x12345u && v[1][3] == 0x777u) ptx::tmem_st_16x128b_x8(a_addr, v[0]);
-#else
-                    ptx::tmem_st_16x128b_x8(a_addr, v[0]);
-                    ptx::tmem_st_16x128b_x8(a_addr + (16u << 16), v[1]);
+                if (mine == 0) {   // nothing of this stage is ours: still take part in the hand-shakes
+                    if (!kUnified && lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);
+                    if (!PROF_WAIT(2, ptx::mbar_wait(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                } else {
                     ptx::tc_wait_st();
-#endif
                     ptx::tc_fence_before_sync();
                 }
                 __syncwarp();
