@@ -43,7 +43,10 @@ namespace {
 #define FPX_KS_SMALL 4
 #endif
 // K blocks (64 wide) per pipeline stage for a given tile width
-constexpr int gemm_ks(int n_tile) { return n_tile <= 32 ? FPX_KS_SMALL : (n_tile <= 128 ? 2 : 1); }
+#ifndef FPX_KS_64
+#define FPX_KS_64 4
+#endif
+constexpr int gemm_ks(int n_tile) { return n_tile <= 32 ? FPX_KS_SMALL : (n_tile <= 64 ? FPX_KS_64 : (n_tile <= 128 ? 2 : 1)); }
 
 constexpr int kTileM = 128;
 constexpr int kAColsPerKBlock = 32;      // 64 fp16 along K per tensor-memory lane
@@ -82,7 +85,7 @@ template <int BW, int N_TILE>
 struct Config {
     using Raw = RawBlock<BW>;
     static constexpr int ks = gemm_ks(N_TILE);
-    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : 5) : (N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 7 : 5)));
+    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : (N_TILE <= 32 ? 5 : 4)) : (N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 7 : 5)));
     static constexpr int a_stages = ks == 4 ? 3 : (N_TILE <= 64 ? 6 : (N_TILE <= 128 ? 4 : 5));
     // when the A ring is as deep as the shared-memory ring one commit frees a whole stage
     static constexpr bool unified = a_stages == stages;
@@ -92,7 +95,7 @@ struct Config {
     // ... of it, so a stage's 16 MMAs are issued in a quarter of the time one thread would need and its ring slots come
     // back that much sooner.  Wider tiles: issuer i takes the stages i, i + issuers, ... whole (measured faster there).
     static constexpr bool split_stage = ks == 4;
-    static constexpr int issuers = split_stage ? 4 : (N_TILE <= 128 ? 2 : 1);
+    static constexpr int issuers = split_stage ? (N_TILE <= 32 ? 4 : 2) : (N_TILE <= 128 ? 2 : 1);
     static constexpr int slot_commits = split_stage ? issuers : 1;   // commits that free a ring slot
     static constexpr int acc_bufs = 1;   // the issuing warps also run the epilogue, so one set of accumulators suffices
     static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
