@@ -348,11 +348,36 @@ def run_ours(args):
             ab = alg_bytes(mdl["oc"], mdl["ic"], bs, bw)
             fl = 2.0 * mdl["oc"] * mdl["ic"] * bs
             t_roof = max(ab / world / (hbm_peak * 1e9), fl / world / (tc_peak * 1e12))
-            per_case.append({"layer": mdl["name"], "oc": mdl["oc"], "ic": mdl["ic"], "bs": bs, "split_k": split[(mdl["name"], bs)],
-                             "us": round(us, 3), "tflops": round(fl / us / 1e6, 3),
-                             "weight_gbs": round(mdl["oc"] * mdl["ic"] * bw / 8 / us / 1e3, 1),
-                             "roofline_frac": round(t_roof / (us * 1e-6), 4)})
+            entry = {"layer": mdl["name"], "oc": mdl["oc"], "ic": mdl["ic"], "bs": bs, "split_k": split[(mdl["name"], bs)],
+                     "us": round(us, 3), "tflops": round(fl / us / 1e6, 3),
+                     "weight_gbs": round(mdl["oc"] * mdl["ic"] * bw / 8 / us / 1e3, 1),
+                     "roofline_frac": round(t_roof / (us * 1e-6), 4)}
             del g, keep
+            if args.compare_cublas and world == 1:
+                # the same layer as a library fp16 GEMM on weights dequantised on the GPU (2.67x / 3.2x the bytes), cold L2
+                w16 = f.dequant_packed_cuda(e, m, mdl["packed"], mdl["scale"])
+                n16 = max(2, -(-target // (w16.numel() * 2)))
+                reps16 = [w16] + [w16.clone() for _ in range(n16 - 1)]
+                x = acts[(mdl["name"], bs)]
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(stream):
+                    torch.nn.functional.linear(x, reps16[0])
+                    torch.cuda.synchronize(dev)
+                    with torch.cuda.graph(g, stream=stream):
+                        keep = [torch.nn.functional.linear(x, w) for w in reps16]
+                    g.replay()
+                    torch.cuda.synchronize(dev)
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    for _ in range(reps):
+                        g.replay()
+                    b.record(stream)
+                torch.cuda.synchronize(dev)
+                us16 = a.elapsed_time(b) * 1e3 / (reps * n16)
+                entry["cublas_fp16_us"] = round(us16, 3)
+                entry["speedup_vs_cublas_fp16"] = round(us16 / us, 3)
+                del g, keep, reps16, w16
+            per_case.append(entry)
 
     # ---- end to end through the host-buffer entry point (single GPU only: it is a per-GPU call)
     e2e = None
@@ -438,6 +463,8 @@ def main():
     ap.add_argument("--split-k", type=int, default=0, help="0 = let the library decompose the work")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused", help="N > 1: how the ranks' rows reach each other")
+    ap.add_argument("--compare-cublas", action="store_true",
+                    help="also time torch's fp16 GEMM on GPU-dequantised weights for every case (single GPU)")
     ap.add_argument("--no-static-weights", action="store_true",
                     help="do not let a GEMM read its (prepacked, read-only) weights before the previous kernel has completed")
     ap.add_argument("--case", default=None, help="LAYER:BATCH - run only this launch shape of the workload (for profiler captures)")

@@ -27,7 +27,7 @@ C_SYMBOLS = (
     "fp6b200_workspace_bytes", "fp6b200_choose_split_k", "fp6b200_prepack", "fp6b200_prepack_host",
     "fp6b200_dequant", "fp6b200_dequant_host", "fp6b200_dequant_packed", "fp6b200_splitk_reduce",
     "fp6b200_device_status", "fp6b200_linear_static_scratch", "fp6b200_static_scratch_bytes",
-    "fp6b200_linear_gather", "fp6b200_set_option", "fp6b200_get_option",
+    "fp6b200_linear_gather", "fp6b200_set_option", "fp6b200_get_option", "fp6b200_quantize_prepack",
 )
 
 
@@ -110,6 +110,8 @@ def lib() -> ctypes.CDLL:
     L.fp6b200_set_option.argtypes = [ci, ci]
     L.fp6b200_get_option.restype = ci
     L.fp6b200_get_option.argtypes = [ci]
+    L.fp6b200_quantize_prepack.restype = ci
+    L.fp6b200_quantize_prepack.argtypes = [ci, ci, vp, vp, vp, vp, sz, sz]
     L.fp6b200_device_status.restype = ci
     L.fp6b200_device_status.argtypes = [ctypes.POINTER(ci)]
     _lib = L

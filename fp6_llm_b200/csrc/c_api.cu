@@ -188,6 +188,13 @@ int fp6b200_prepack(int e_bits, int m_bits, void* stream, const void* unpacked_d
     return fpx::launch_prepack(e_bits, m_bits, static_cast<cudaStream_t>(stream), unpacked_dev, packed_dev, M, K);
 }
 
+int fp6b200_quantize_prepack(int e_bits, int m_bits, void* stream, const void* weights_fp16_dev, const void* scales_dev,
+                             void* packed_dev, size_t M, size_t K) {
+    return fpx::launch_quantize_prepack(e_bits, m_bits, static_cast<cudaStream_t>(stream),
+                                        static_cast<const __half*>(weights_fp16_dev), static_cast<const __half*>(scales_dev),
+                                        packed_dev, M, K);
+}
+
 int fp6b200_prepack_host(int e_bits, int m_bits, int* packed_host, const int* unpacked_host, size_t M, size_t K) {
     if (!fpx::format_supported(e_bits, m_bits) || !packed_host || !unpacked_host || M % 64 || K % 64 || !M || !K)
         return cudaErrorInvalidValue;

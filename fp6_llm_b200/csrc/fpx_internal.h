@@ -48,6 +48,9 @@ int* gemm_status_word();
 // Weight format kernels.  All pointers are device pointers; in != out.
 cudaError_t launch_prepack(int e_bits, int m_bits, cudaStream_t stream, const void* unpacked, void* packed, size_t M,
                            size_t K);
+// fp16 weights [M][K] + fp16 row scales -> prepacked FPx (round to nearest, ties to the even code, saturating).
+cudaError_t launch_quantize_prepack(int e_bits, int m_bits, cudaStream_t stream, const __half* weights,
+                                    const __half* scales, void* packed, size_t M, size_t K);
 cudaError_t launch_dequant_unpacked(int e_bits, int m_bits, cudaStream_t stream, const void* unpacked,
                                     const __half* scales, __half* out, size_t M, size_t K);
 cudaError_t launch_dequant_packed(int e_bits, int m_bits, cudaStream_t stream, const void* packed,

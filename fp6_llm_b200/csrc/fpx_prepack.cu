@@ -72,6 +72,82 @@ prepack_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32
     }
 }
 
+// Round-to-nearest quantiser fused with the packer: fp16 weights [M, K] and fp16 row scales in, prepacked FPx out,
+// without the unpacked tensor in between.  (The reference ships no working quantiser: fp6_llm/csrc/utils/
+// weight_quant.h:9-104 truncates and is not bound; the layout it would feed is the packer's above.)
+// Code of a weight = nearest representable magnitude of |w / scale| (the division in fp32, round to nearest);
+// ties go to the even code; beyond the largest magnitude it saturates; the sign bit is the sign of the quotient.
+template <int E_BITS>
+__device__ __forceinline__ float fpx_magnitude(int c) {   // value of the non-negative code c (2 mantissa bits)
+    constexpr int kBias = (1 << (E_BITS - 1)) - 1;
+    const int e = c >> 2, m = c & 3;
+    return e == 0 ? (float)m * exp2f((float)(1 - kBias - 2)) : (float)(4 + m) * exp2f((float)(e - kBias - 2));
+}
+template <int E_BITS>
+__device__ __forceinline__ uint32_t quantize_rtn_code(float q) {
+    constexpr int kCodes = 1 << (E_BITS + 2);
+    const float a = fabsf(q);
+    int below = 0, not_above = 0;   // midpoints < a, midpoints <= a
+#pragma unroll
+    for (int c = 0; c + 1 < kCodes; c++) {
+        const float mid = 0.5f * (fpx_magnitude<E_BITS>(c) + fpx_magnitude<E_BITS>(c + 1));   // folded at compile time
+        below += mid < a ? 1 : 0;
+        not_above += mid <= a ? 1 : 0;
+    }
+    const uint32_t mag = (uint32_t)((below & 1) ? not_above : below);   // they differ only on an exact tie
+    return mag | (signbit(q) ? (uint32_t)kCodes : 0u);
+}
+
+template <int BW>
+__global__ void __launch_bounds__(kPrepackThreads)
+quantize_prepack_kernel(const __half* __restrict__ w, const __half* __restrict__ scales, uint8_t* __restrict__ out,
+                        uint32_t M, uint32_t K) {
+    constexpr int E_BITS = BW - 3;
+    constexpr uint32_t kCols = kChunkKBlocks * kKBlock;
+    constexpr uint32_t kPitch = kCols + 4;
+    __shared__ __align__(16) uint8_t codes[kRowsPerBlock * kPitch];
+
+    const uint32_t kblocks = K / kKBlock;
+    const uint32_t chunks_per_row = (kblocks + kChunkKBlocks - 1) / kChunkKBlocks;
+    const uint32_t i = blockIdx.x / chunks_per_row;            // 64-row block
+    const uint32_t kb0 = (blockIdx.x % chunks_per_row) * kChunkKBlocks;
+    const uint32_t nkb = min((uint32_t)kChunkKBlocks, kblocks - kb0);
+    const uint32_t ncols = nkb * kKBlock;
+    const uint32_t col0 = kb0 * kKBlock;
+
+    for (uint32_t x = threadIdx.x; x < kRowsPerBlock * (ncols / 2); x += kPrepackThreads) {   // two weights per thread and round
+        const uint32_t r = x / (ncols / 2), c = (x % (ncols / 2)) * 2;
+        const uint32_t row = i * kRowsPerBlock + r;
+        const __half2 pair = *reinterpret_cast<const __half2*>(w + (size_t)row * K + col0 + c);
+        const float sc = __half2float(scales[row]);
+        codes[r * kPitch + c] = (uint8_t)quantize_rtn_code<E_BITS>(__fdiv_rn(__low2float(pair), sc));
+        codes[r * kPitch + c + 1] = (uint8_t)quantize_rtn_code<E_BITS>(__fdiv_rn(__high2float(pair), sc));
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int wd = 1; wd <= 4; wd <<= 1) {
+        if (!has_seg(BW, wd)) continue;
+        const int shift = seg_shift(BW, wd);
+        const uint32_t words_per_tile = 4u * wd * 32u;
+        uint32_t* region = reinterpret_cast<uint32_t*>(out + region_offset(BW, wd, M, K));
+        for (uint32_t x = threadIdx.x; x < nkb * words_per_tile; x += kPrepackThreads) {
+            const uint32_t kb = kb0 + x / words_per_tile;
+            const uint32_t in_tile = x % words_per_tile;
+            const int lane = in_tile & 31;
+            const uint64_t word_in_lane = ((uint64_t)i * kblocks + kb) * (4u * wd) + (in_tile >> 5);
+            uint32_t word = 0;
+#pragma unroll 8
+            for (int pos = 0; pos < 32 / wd; pos++) {
+                const FieldSource src = field_source(wd, word_in_lane, lane, pos, K);
+                const uint32_t code = codes[(src.row - i * kRowsPerBlock) * kPitch + (src.col - col0)];
+                word |= ((code >> shift) & ((1u << wd) - 1u)) << (32 - (pos + 1) * wd);
+            }
+            region[word_in_lane * 32 + lane] = word;
+        }
+    }
+}
+
 // Thread = 8 consecutive codes of one row (BW bytes in, 16 bytes out).
 template <int BW>
 __global__ void __launch_bounds__(256)
@@ -161,6 +237,22 @@ cudaError_t launch_prepack(int e_bits, int m_bits, cudaStream_t stream, const vo
         prepack_kernel<6><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K);
     else
         prepack_kernel<5><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_prepack(int e_bits, int m_bits, cudaStream_t stream, const __half* weights,
+                                    const __half* scales, void* packed, size_t M, size_t K) {
+    if (!shape_ok(e_bits, m_bits, M, K) || !weights || !scales || !packed) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(weights) & 3) || (reinterpret_cast<uintptr_t>(packed) & 3))
+        return cudaErrorMisalignedAddress;
+    const size_t kblocks = K / kKBlock;
+    const size_t blocks = (M / kRowsPerBlock) * ((kblocks + kChunkKBlocks - 1) / kChunkKBlocks);
+    if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+    uint8_t* out = static_cast<uint8_t*>(packed);
+    if (e_bits == 3)
+        quantize_prepack_kernel<6><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(weights, scales, out, (uint32_t)M, (uint32_t)K);
+    else
+        quantize_prepack_kernel<5><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(weights, scales, out, (uint32_t)M, (uint32_t)K);
     return cudaGetLastError();
 }
 

@@ -1,0 +1,61 @@
+"""A torch.nn.Module around the FPx linear layer, the form in which inference engines use the reference's kernel
+(the reference's README points to DeepSpeed's FP6 linear module, README.md:19,235; the reference itself ships only the
+functional operators of fp6_llm/__init__.py).
+
+    layer = FPxLinear.from_linear(torch_linear, e_bits=3, m_bits=2)     # quantise (RTN, per-row scale) + prepack on the GPU
+    y = layer(x)                                                        # x [..., IC] fp16 -> [..., OC] fp16
+"""
+from __future__ import annotations
+
+import torch
+
+from .formats import bit_width, check_format, magnitudes
+from .ops import linear_forward_eXmY_cuda, quantize_prepack_cuda
+
+
+class FPxLinear(torch.nn.Module):
+    """y = x @ dequant(W)^T (+ bias) with W held as prepacked FP6 (e3m2) / FP5 (e2m2) codes and fp16 row scales."""
+
+    def __init__(self, packed: torch.Tensor, scales: torch.Tensor, bias: torch.Tensor | None = None, e_bits: int = 3,
+                 m_bits: int = 2, split_k: int = 0):
+        super().__init__()
+        check_format(e_bits, m_bits)
+        if packed.dtype != torch.int32 or packed.dim() != 2 or scales.dtype != torch.float16:
+            raise ValueError("expected prepacked int32 weights [OC, IC/32*bw] and fp16 scales [OC]")
+        if scales.numel() != packed.shape[0] or (bias is not None and bias.numel() != packed.shape[0]):
+            raise ValueError("scales and bias need one entry per output channel")
+        self.e_bits, self.m_bits, self.split_k = e_bits, m_bits, split_k
+        self.out_features = packed.shape[0]
+        self.in_features = packed.shape[1] * 32 // bit_width(e_bits, m_bits)
+        self.register_buffer("weight", packed)
+        self.register_buffer("scales", scales)
+        self.register_buffer("bias", bias.to(torch.float16) if bias is not None else None)
+
+    @staticmethod
+    def row_scales(weight: torch.Tensor, e_bits: int, m_bits: int) -> torch.Tensor:
+        """max|w| of each output channel mapped to the format's largest magnitude (28 for e3m2, 7 for e2m2)."""
+        top = float(magnitudes(e_bits, m_bits)[-1])
+        return (weight.float().abs().amax(dim=1) / top).clamp_min(2.0 ** -24).to(torch.float16)
+
+    @classmethod
+    def from_linear(cls, linear: torch.nn.Linear, e_bits: int = 3, m_bits: int = 2, split_k: int = 0) -> "FPxLinear":
+        """Quantise a (CUDA) torch.nn.Linear: per-row scale, round to nearest, prepacked by one kernel."""
+        w = linear.weight.detach().to(torch.float16).contiguous()
+        if not w.is_cuda:
+            raise ValueError("the layer must live on a CUDA device: quantisation and packing run there")
+        scales = cls.row_scales(w, e_bits, m_bits)
+        packed = quantize_prepack_cuda(w, scales, e_bits, m_bits)
+        bias = linear.bias.detach() if linear.bias is not None else None
+        return cls(packed, scales, bias, e_bits, m_bits, split_k)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dtype != torch.float16 or x.shape[-1] != self.in_features:
+            raise ValueError(f"expected fp16 activations [..., {self.in_features}]")
+        flat = x.reshape(-1, self.in_features).contiguous()
+        y = linear_forward_eXmY_cuda(self.e_bits, self.m_bits, flat, self.weight, self.scales, self.split_k)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*x.shape[:-1], self.out_features)
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, format=e{self.e_bits}m{self.m_bits}"

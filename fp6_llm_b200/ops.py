@@ -159,6 +159,29 @@ def weight_prepacking_eXmY_cpu(EXPONENT: int, MANTISSA: int, fpx_tensor: torch.T
     return out
 
 
+def quantize_prepack_cuda(weights: torch.Tensor, scales: torch.Tensor, EXPONENT: int = 3, MANTISSA: int = 2) -> torch.Tensor:
+    """fp16 CUDA weights [OC, IC] and fp16 row scales [OC] -> prepacked int32 [OC, IC/32*bw] in one kernel: round to
+    nearest (ties to the even code, saturating) and the reference's packed layout
+    (fp6_llm/csrc/utils/weight_prepacking.h:118-196).  Same bits as quantising with formats.quantize_rtn, packing the
+    codes and prepacking them.  The reference has no bound quantiser (fp6_llm/csrc/utils/weight_quant.h is unused)."""
+    _require_cuda()
+    check_format(EXPONENT, MANTISSA)
+    if weights.dtype != torch.float16 or scales.dtype != torch.float16 or not (weights.is_cuda and scales.is_cuda):
+        raise ValueError("expected fp16 CUDA weights and scales")
+    if weights.dim() != 2 or scales.numel() != weights.shape[0]:
+        raise ValueError("expected weights [OC, IC] and one scale per output channel")
+    OC, IC = weights.shape
+    if OC % 256 or IC % 64:
+        raise ValueError("need OC % 256 == 0 and IC % 64 == 0")
+    src, sc = weights.contiguous(), scales.contiguous()
+    out = torch.empty((OC, IC * bit_width(EXPONENT, MANTISSA) // 32), dtype=torch.int32, device=weights.device)
+    with torch.cuda.device(weights.device):
+        rc = _native.lib().fp6b200_quantize_prepack(EXPONENT, MANTISSA, _stream_ptr(weights.device), _ptr(src), _ptr(sc),
+                                                    _ptr(out), OC, IC)
+    _native.check(rc, "fp6b200_quantize_prepack")
+    return out
+
+
 def weight_prepacking_cpu(fp6_tensor: torch.Tensor) -> torch.Tensor:
     """FP6 case of :func:`weight_prepacking_eXmY_cpu` (weight_matrix_prepacking_cpu, fp6_llm/csrc/fp6_linear.cu:211-223)."""
     return weight_prepacking_eXmY_cpu(3, 2, fp6_tensor)

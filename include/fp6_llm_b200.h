@@ -62,6 +62,17 @@ size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k);
 int fp6b200_choose_split_k(size_t M, size_t N, size_t K, int num_sms);
 
 /*
+ * fp16 weights [M][K] and fp16 row scales -> prepacked FPx weights in one pass on the device (the step before
+ * prepacking when a checkpoint is loaded).  The reference has no working counterpart: its quantiser
+ * (fp6_llm/csrc/utils/weight_quant.h:9-104) truncates and is not bound to Python; the output layout is the packer's
+ * (fp6_llm/csrc/utils/weight_prepacking.h:118-196).  A weight becomes the code whose magnitude is nearest to
+ * |w / scale| (fp32 division), ties to the even code, saturating at the largest magnitude, sign of the quotient.
+ * Needs M % 64 == 0 and K % 64 == 0.
+ */
+int fp6b200_quantize_prepack(int e_bits, int m_bits, void* stream, const void* weights_fp16_dev, const void* scales_dev,
+                             void* packed_dev, size_t M, size_t K);
+
+/*
  * Weight prepacking on device buffers (in != out), asynchronous on `stream`.
  * GPU counterpart of weight_matrix_prepacking_fp_eXmY (fp6_llm/csrc/utils/weight_prepacking.h:204-211);
  * the output is bit-identical.  Needs M % 64 == 0 and K % 64 == 0 (:121-122).

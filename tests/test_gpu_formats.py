@@ -118,3 +118,32 @@ def test_splitk_reduce_kernel(native_lib, oracle_mod):
     assert native_lib.fp6b200_splitk_reduce(None, out.data_ptr(), d.data_ptr(), 3 * 512, 7) == 0
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy().view(np.uint16), oracle_mod.splitk_reduce(p).view(np.uint16))
+
+
+@pytest.mark.parametrize("e,m", FORMATS)
+def test_quantize_prepack_matches_quantiser_then_packer(native_lib, e, m):
+    """The fused kernel gives the bits of: round-to-nearest codes (formats.quantize_rtn) -> bit stream -> prepack.
+    The inputs include exact ties between neighbouring magnitudes, values beyond the largest magnitude, signed
+    zeros and fp16 subnormals."""
+    import fp6_llm_b200 as f
+    from fp6_llm_b200.formats import magnitudes, pack_codes, quantize_rtn
+    gen = torch.Generator().manual_seed(7 + e)
+    oc, ic = 512, 320
+    w = (torch.randn(oc, ic, generator=gen) * 0.05).half()
+    mag = magnitudes(e, m)
+    scale = (w.float().abs().amax(dim=1) / mag[-1]).half()         # the usual per-row scale: nothing saturates by much
+    mids = ((mag[:-1] + mag[1:]) * 0.5).half()                      # every midpoint is exact in fp16
+    scale[:8] = 1.0                                                 # rows with scale 1: the values below are the quotients
+    w[0, : mids.numel()] = mids
+    w[1, : mids.numel()] = -mids
+    w[2, :4] = torch.tensor([0.0, -0.0, 6.0e-8, -6.0e-8]).half()
+    w[3, :4] = torch.tensor([1000.0, -1000.0, float(mag[-1]), -float(mag[-1])]).half()
+    w[4, : mag.numel()] = mag.half()
+    expect = f.weight_prepacking_eXmY_cpu(e, m, pack_codes(quantize_rtn(w, scale, e, m), e, m).cuda())
+    got = f.quantize_prepack_cuda(w.cuda(), scale.cuda(), e, m)
+    assert torch.equal(got, expect)
+    # and the packed result dequantises to within half a step of the input
+    back = f.dequant_packed_cuda(e, m, got, scale.cuda()).float().cpu()
+    step = (mag[1:] - mag[:-1]).max()
+    body = w[8:].float()
+    assert ((back[8:] - body).abs() <= 0.51 * step * scale[8:].float()[:, None] + 1e-6).all()

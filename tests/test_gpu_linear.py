@@ -181,3 +181,24 @@ def test_static_weights_option_gives_identical_results(native_lib):
         f.set_static_weights(False)
     assert native_lib.fp6b200_set_option(99, 1) == 1         # unknown option: cudaErrorInvalidValue
     assert native_lib.fp6b200_get_option(99) == -1
+
+
+def test_module_wrapper_matches_dequantised_linear(native_lib):
+    """FPxLinear.from_linear quantises and packs on the GPU; its output equals the fp32 matmul on the dequantised
+    weights (plus bias) within the linear layer's tolerance, for batched inputs of any leading shape."""
+    import fp6_llm_b200 as f
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(1024, 512, bias=True).cuda().half()
+    layer = f.FPxLinear.from_linear(lin)
+    assert (layer.in_features, layer.out_features) == (1024, 512)
+    x = torch.randn(3, 5, 1024, device="cuda").half()
+    y = layer(x)
+    assert y.shape == (3, 5, 512) and y.dtype == torch.float16
+    w16 = f.dequant_packed_cuda(3, 2, layer.weight, layer.scales).float()
+    ref = x.float().reshape(-1, 1024) @ w16.T + lin.bias.float()
+    err = (y.float().reshape(-1, 512) - ref).norm() / ref.norm()
+    assert err.item() <= 2e-3
+    # the quantised layer stays close to the fp16 layer it came from (6-bit weights: a few percent)
+    full = lin(x).float()
+    assert ((y.float() - full).norm() / full.norm()).item() < 0.06
+    assert f.device_status() == 0
