@@ -15,6 +15,7 @@
 //     the top w bits of every byte and then shifting left by w walks the codes in use order.
 #pragma once
 #include <stdint.h>
+#include <string.h>
 
 #if defined(__CUDACC__)
 #define FPX_HD __host__ __device__ __forceinline__
@@ -145,6 +146,36 @@ FPX_HD void unpack16(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, int h
     }
     out[0] = expand_13(y0); out[1] = expand_02(y0); out[2] = expand_13(y1); out[3] = expand_02(y1);
     out[4] = expand_13(y2); out[5] = expand_02(y2); out[6] = expand_13(y3); out[7] = expand_02(y3);
+}
+
+// Round-to-nearest quantiser (2 mantissa bits).  Value of the non-negative code c: subnormals m/4 * 2^(1-bias),
+// otherwise (1 + m/4) * 2^(e-bias), bias = 2^(E-1) - 1 (28 is the largest e3m2 magnitude, 7 the largest e2m2 one).
+FPX_HD float fpx_magnitude(int e_bits, int c) {
+    const int bias = (1 << (e_bits - 1)) - 1;
+    const int e = c >> 2, m = c & 3;
+    const int p = (e == 0 ? 1 : e) - bias - 2;               // the value is (e == 0 ? m : 4 + m) * 2^p
+    const float unit = p >= 0 ? (float)(1 << p) : 1.0f / (float)(1 << -p);
+    return (float)(e == 0 ? m : 4 + m) * unit;
+}
+// Code (sign bit included) of the quotient q = w / scale: the nearest magnitude, ties to the even code, saturating;
+// the sign bit is the sign bit of q (so -0 keeps its sign).
+FPX_HD uint32_t quantize_rtn_code(int e_bits, float q) {
+    const int codes = 1 << (e_bits + 2);
+    const float a = q < 0.0f ? -q : q;
+    int below = 0, not_above = 0;                            // midpoints < a, midpoints <= a
+    for (int c = 0; c + 1 < codes; c++) {
+        const float mid = 0.5f * (fpx_magnitude(e_bits, c) + fpx_magnitude(e_bits, c + 1));
+        below += mid < a ? 1 : 0;
+        not_above += mid <= a ? 1 : 0;
+    }
+    const uint32_t mag = (uint32_t)((below & 1) ? not_above : below);   // they differ only on an exact tie
+    uint32_t bits;
+#if defined(__CUDA_ARCH__)
+    bits = __float_as_uint(q);
+#else
+    memcpy(&bits, &q, sizeof(bits));
+#endif
+    return mag | ((bits >> 31) ? (uint32_t)codes : 0u);
 }
 
 // 2^(16 - 2^(E-1)) as an fp16 bit pattern: 2^12 for E=3, 2^14 for E=2

@@ -77,27 +77,6 @@ prepack_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32
 // weight_quant.h:9-104 truncates and is not bound; the layout it would feed is the packer's above.)
 // Code of a weight = nearest representable magnitude of |w / scale| (the division in fp32, round to nearest);
 // ties go to the even code; beyond the largest magnitude it saturates; the sign bit is the sign of the quotient.
-template <int E_BITS>
-__device__ __forceinline__ float fpx_magnitude(int c) {   // value of the non-negative code c (2 mantissa bits)
-    constexpr int kBias = (1 << (E_BITS - 1)) - 1;
-    const int e = c >> 2, m = c & 3;
-    return e == 0 ? (float)m * exp2f((float)(1 - kBias - 2)) : (float)(4 + m) * exp2f((float)(e - kBias - 2));
-}
-template <int E_BITS>
-__device__ __forceinline__ uint32_t quantize_rtn_code(float q) {
-    constexpr int kCodes = 1 << (E_BITS + 2);
-    const float a = fabsf(q);
-    int below = 0, not_above = 0;   // midpoints < a, midpoints <= a
-#pragma unroll
-    for (int c = 0; c + 1 < kCodes; c++) {
-        const float mid = 0.5f * (fpx_magnitude<E_BITS>(c) + fpx_magnitude<E_BITS>(c + 1));   // folded at compile time
-        below += mid < a ? 1 : 0;
-        not_above += mid <= a ? 1 : 0;
-    }
-    const uint32_t mag = (uint32_t)((below & 1) ? not_above : below);   // they differ only on an exact tie
-    return mag | (signbit(q) ? (uint32_t)kCodes : 0u);
-}
-
 template <int BW>
 __global__ void __launch_bounds__(kPrepackThreads)
 quantize_prepack_kernel(const __half* __restrict__ w, const __half* __restrict__ scales, uint8_t* __restrict__ out,
@@ -120,8 +99,8 @@ quantize_prepack_kernel(const __half* __restrict__ w, const __half* __restrict__
         const uint32_t row = i * kRowsPerBlock + r;
         const __half2 pair = *reinterpret_cast<const __half2*>(w + (size_t)row * K + col0 + c);
         const float sc = __half2float(scales[row]);
-        codes[r * kPitch + c] = (uint8_t)quantize_rtn_code<E_BITS>(__fdiv_rn(__low2float(pair), sc));
-        codes[r * kPitch + c + 1] = (uint8_t)quantize_rtn_code<E_BITS>(__fdiv_rn(__high2float(pair), sc));
+        codes[r * kPitch + c] = (uint8_t)quantize_rtn_code(E_BITS, __fdiv_rn(__low2float(pair), sc));
+        codes[r * kPitch + c + 1] = (uint8_t)quantize_rtn_code(E_BITS, __fdiv_rn(__high2float(pair), sc));
     }
     __syncthreads();
 

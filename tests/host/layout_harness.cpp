@@ -146,4 +146,9 @@ int harness_check_plan(uint32_t mode, uint32_t m_tiles, uint32_t n_tiles, uint32
     return 0;
 }
 
-}  // extern "C"
+
+// Codes of n quotients, as the fused quantise + pack kernel computes them.
+void harness_quantize(int e_bits, const float* q, int n, unsigned char* codes) {
+    for (int i = 0; i < n; i++) codes[i] = (unsigned char)fpx::quantize_rtn_code(e_bits, q[i]);
+}
+}

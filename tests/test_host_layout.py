@@ -74,3 +74,24 @@ def test_work_plans_cover_every_unit_once(harness):
                 assert harness.harness_check_plan(mode, mt, nt, kb, sk, grid) == 0, (mode, mt, nt, kb, sk, grid)
                 n += 1
     assert n > 1000
+
+
+@pytest.mark.parametrize("e,m", FORMATS)
+def test_quantiser_matches_the_tensor_quantiser(harness, e, m):
+    """The scalar round-to-nearest routine of the fused quantise + pack kernel against formats.quantize_rtn, on random
+    quotients, on every magnitude, on every exact tie between neighbours, beyond the largest magnitude and on signed
+    zeros."""
+    import torch
+    from fp6_llm_b200.formats import magnitudes, quantize_rtn
+    mag = magnitudes(e, m)
+    mids = (mag[:-1] + mag[1:]) * 0.5
+    gen = torch.Generator().manual_seed(11 + e)
+    q = torch.cat([torch.randn(20000, generator=gen) * float(mag[-1]) * 0.5, mag, -mag, mids, -mids,
+                   torch.nextafter(mids, torch.tensor(0.0)), torch.nextafter(mids, torch.tensor(1e9)),
+                   torch.tensor([0.0, -0.0, 1e-30, -1e-30, 1e6, -1e6, float(mag[-1]) * 1.0001])]).float().contiguous()
+    expect = quantize_rtn(q[None, :], torch.ones(1), e, m)[0].numpy()
+    got = np.zeros(q.numel(), np.uint8)
+    harness.harness_quantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    harness.harness_quantize.restype = None
+    harness.harness_quantize(e, ctypes.c_void_p(q.numpy().ctypes.data), q.numel(), ctypes.c_void_p(got.ctypes.data))
+    assert np.array_equal(got, expect)
