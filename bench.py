@@ -47,7 +47,7 @@ FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, averaged over the launches of one step, from the ncu
 # launch list of this command (profiles/launch_list_llama2-7b-fp6_bench_step.md).  A recorded figure, not measured live.
-NCU_TRAFFIC_BYTES = {"llama2-7b-fp6": 38.52e6}
+NCU_TRAFFIC_BYTES = {"llama2-7b-fp6": 38.53e6}
 
 
 def alg_bytes(oc, ic, bs, bw):
