@@ -407,11 +407,20 @@ def run_ours(args):
     # ---- CPU baseline (rank 0, single GPU run only): bounded sample of the same workload
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        layer = min(layers, key=lambda l: l[1] * l[2])
-        rows = cpu_sample_rows(e, m, layer, batches, 1, budget_s=15.0)
-        fl, secs, deq, kind = cpu_reference_step(e, m, layer, batches, rows)
+        # every layer of the workload at every batch size, cut to the same fraction of its output channels so that
+        # the whole sample takes about 20 s
+        _, probe_s, _, _ = cpu_reference_step(e, m, layers[0], batches, rows=64)
+        est = probe_s / (64 * layers[0][2]) * sum(l[1] * l[2] for l in layers)
+        frac = min(1.0, 20.0 / max(est, 1e-9))
+        fl = secs = deq = 0.0
+        parts = []
+        for layer in layers:
+            rows = max(64, int(layer[1] * frac) // 64 * 64)
+            f_l, s_l, d_l, kind = cpu_reference_step(e, m, layer, batches, rows)
+            fl, secs, deq = fl + f_l, secs + s_l, deq + d_l
+            parts.append(f"{layer[0]} {rows}/{layer[1]}")
         cpu = {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
-               "sample": f"one pass over the first {rows} output channels of layer {layer[0]} {layer[1]}x{layer[2]} at batch sizes "
+               "sample": f"one pass over the first output channels of every layer ({', '.join(parts)}) at batch sizes "
                          f"{batches}: {secs:.2f} s, of which single-threaded dequantisation {deq:.2f} s"}
 
     if rank == 0:
