@@ -324,7 +324,7 @@ def run_ours(args):
 
     # ---- per-case device times (separate pass, each case alone in a graph of `replicas` launches)
     per_case = []
-    if rank == 0 or world > 1:
+    if world == 1 or args.per_case_multi:
         for mdl, bs in cases:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.stream(stream):
@@ -472,6 +472,8 @@ def main():
     ap.add_argument("--split-k", type=int, default=0, help="0 = let the library decompose the work")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused", help="N > 1: how the ranks' rows reach each other")
+    ap.add_argument("--per-case-multi", action="store_true",
+                    help="N > 1: also time every (layer, batch) pair alone (off by default: the step time is the result)")
     ap.add_argument("--compare-cublas", action="store_true",
                     help="also time torch's fp16 GEMM on GPU-dequantised weights for every case (single GPU)")
     ap.add_argument("--no-static-weights", action="store_true",

@@ -736,7 +736,11 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params
     // failure whose cause has not been found; that configuration keeps plain stream order between launches.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+#ifdef FPX_NO_PDL
+    attr[0].val.programmaticStreamSerializationAllowed = 0;
+#else
     attr[0].val.programmaticStreamSerializationAllowed = N_TILE <= 128 ? 1 : 0;
+#endif
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, map, prm);
