@@ -254,6 +254,7 @@ def run_ours(args):
     # of the stream is still finishing (see fp6b200_set_option in include/fp6_llm_b200.h).
     torch.cuda.synchronize(dev)
     f.set_static_weights(not args.no_static_weights)
+    f.set_programmatic_launch(not args.no_programmatic_launch)
     acts = {(mdl["name"], bs): torch.randn(bs, mdl["ic"], device=dev, dtype=torch.float16) for mdl in models for bs in batches}
     cases = [(mdl, bs) for bs in batches for mdl in models]
     # split_k = 0: the library decomposes the work itself (tile waves + stream-K remainder + fix-up kernel)
@@ -476,6 +477,8 @@ def main():
                     help="N > 1: also time every (layer, batch) pair alone (off by default: the step time is the result)")
     ap.add_argument("--compare-cublas", action="store_true",
                     help="also time torch's fp16 GEMM on GPU-dequantised weights for every case (single GPU)")
+    ap.add_argument("--no-programmatic-launch", action="store_true",
+                    help="plain stream order between a GEMM and the kernel before it")
     ap.add_argument("--no-static-weights", action="store_true",
                     help="do not let a GEMM read its (prepacked, read-only) weights before the previous kernel has completed")
     ap.add_argument("--case", default=None, help="LAYER:BATCH - run only this launch shape of the workload (for profiler captures)")

@@ -105,12 +105,17 @@ int fp6b200_version(void) { return 1; }
 const char* fp6b200_error_string(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }
 
 int fp6b200_set_option(int option, int value) {
-    if (option != FP6B200_OPTION_STATIC_WEIGHTS) return cudaErrorInvalidValue;
-    fpx::set_weights_static(value);
+    if (option == FP6B200_OPTION_STATIC_WEIGHTS) fpx::set_weights_static(value);
+    else if (option == FP6B200_OPTION_PROGRAMMATIC_LAUNCH) fpx::set_programmatic_launch(value);
+    else return cudaErrorInvalidValue;
     return cudaSuccess;
 }
 
-int fp6b200_get_option(int option) { return option == FP6B200_OPTION_STATIC_WEIGHTS ? fpx::weights_static() : -1; }
+int fp6b200_get_option(int option) {
+    if (option == FP6B200_OPTION_STATIC_WEIGHTS) return fpx::weights_static();
+    if (option == FP6B200_OPTION_PROGRAMMATIC_LAUNCH) return fpx::programmatic_launch();
+    return -1;
+}
 
 int fp6b200_choose_split_k(size_t M, size_t N, size_t K, int num_sms) { return choose_split_k(M, N, K, num_sms); }
 

@@ -736,11 +736,7 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params
     // failure whose cause has not been found; that configuration keeps plain stream order between launches.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-#ifdef FPX_NO_PDL
-    attr[0].val.programmaticStreamSerializationAllowed = 0;
-#else
-    attr[0].val.programmaticStreamSerializationAllowed = N_TILE <= 128 ? 1 : 0;
-#endif
+    attr[0].val.programmaticStreamSerializationAllowed = (N_TILE <= 128 && programmatic_launch()) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, map, prm);
@@ -806,6 +802,9 @@ cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* 
 static std::atomic<int> g_weights_static{0};
 void set_weights_static(int on) { g_weights_static.store(on ? 1 : 0); }
 int weights_static() { return g_weights_static.load(); }
+static std::atomic<int> g_programmatic_launch{1};
+void set_programmatic_launch(int on) { g_programmatic_launch.store(on ? 1 : 0); }
+int programmatic_launch() { return g_programmatic_launch.load(); }
 
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
@@ -901,7 +900,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        const int early = n_tile <= 128 ? 1 : 0;   // wide tiles: plain stream order all the way (see launch_one)
+        const int early = (n_tile <= 128 && programmatic_launch()) ? 1 : 0;   // wide tiles: plain stream order all the way (see launch_one)
         return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan, early);
     }
     if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true);

@@ -37,6 +37,10 @@ cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* 
 // reads them; the GEMM then requests them before the previous kernel of its stream has completed.  Off by default.
 void set_weights_static(int on);
 int weights_static();
+// Whether a GEMM may start while the previous kernel of its stream is finishing (programmatic dependent launch) and
+// whether the fix-up kernel lets the kernel after it do the same.  On by default.
+void set_programmatic_launch(int on);
+int programmatic_launch();
 int gemm_n_tile(size_t N);
 int device_sm_count();
 // Workspace the GEMM needs when it picks its own decomposition (split_k == 0).

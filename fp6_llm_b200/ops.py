@@ -260,6 +260,11 @@ def set_static_weights(on: bool) -> None:
     _native.check(_native.lib().fp6b200_set_option(1, 1 if on else 0), "fp6b200_set_option")
 
 
+def set_programmatic_launch(on: bool) -> None:
+    """Let (default) or do not let a GEMM start while the previous kernel of its stream is finishing."""
+    _native.check(_native.lib().fp6b200_set_option(2, 1 if on else 0), "fp6b200_set_option")
+
+
 def static_weights() -> bool:
     return _native.lib().fp6b200_get_option(1) == 1
 

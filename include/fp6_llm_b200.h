@@ -156,8 +156,13 @@ int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weig
  * With the option on, a prepack (or any write of the weights) must be followed by a synchronisation or an event wait
  * before the first GEMM that reads them.  fp6b200_set_option returns cudaErrorInvalidValue for an unknown option;
  * fp6b200_get_option returns the value, or -1.
+ * FP6B200_OPTION_PROGRAMMATIC_LAUNCH (default 1): the GEMM is launched with programmatic stream serialisation, so that
+ * it starts and sets itself up while the previous kernel of the stream is finishing (it still waits for that kernel
+ * to complete before it touches memory the kernel may have written).  0 restores plain stream order between a GEMM
+ * and whatever precedes it.
  */
 #define FP6B200_OPTION_STATIC_WEIGHTS 1
+#define FP6B200_OPTION_PROGRAMMATIC_LAUNCH 2
 int fp6b200_set_option(int option, int value);
 int fp6b200_get_option(int option);
 
