@@ -85,8 +85,14 @@ template <int BW, int N_TILE>
 struct Config {
     using Raw = RawBlock<BW>;
     static constexpr int ks = gemm_ks(N_TILE);
-    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : (N_TILE <= 32 ? 5 : 4)) : (N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 7 : 5)));
-    static constexpr int a_stages = ks == 4 ? 3 : (N_TILE <= 64 ? 6 : (N_TILE <= 128 ? 4 : 5));
+    // Ring depths.  An mbarrier only tells the parity of its phase, so a waiter must know that the phase before the one
+    // it waits for is complete.  A role that visits only every n-th stage (an unpack team, an issuer that takes whole
+    // stages) knows this when it comes back to a slot on the slot's very next use, i.e. when the ring depth is a
+    // multiple of n; the landing of two copies, unlike the completion of MMAs, is not ordered in time.  (With depth 5
+    // and four teams a warp that came back to a slot four uses later took a copy that had not landed yet for done and
+    // unpacked the slot's previous contents.)
+    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : 4) : (N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 8 : 4)));
+    static constexpr int a_stages = ks == 4 ? 3 : (N_TILE <= 64 ? 6 : 4);
     // when the A ring is as deep as the shared-memory ring one commit frees a whole stage
     static constexpr bool unified = a_stages == stages;
     // One thread can issue an MMA only every ~60-90 cycles, far more than a narrow MMA needs on the tensor
@@ -114,13 +120,14 @@ struct Config {
     static constexpr int groups_per_team = kDequantGroups / teams;
     static constexpr int kb_per_warp = ks / groups_per_team;
     static_assert(kDequantGroups % teams == 0 && ks % groups_per_team == 0 && kb_per_warp >= 1, "unpack work split");
+    static_assert(stages % teams == 0, "an unpack team must meet a shared-memory slot again on the slot's next use");
     static constexpr int readers = 4 * groups_per_team;   // unpack warps per stage
     // An issuer waits on a ring slot only every `issuers` stages.  A parity wait is only meaningful when the
     // slot's previous phase is already complete, which the issuer knows from its own previous wait as long as
     // the rings are at least `issuers` deep.
     static_assert(issuers <= kMaxIssuers, "issuing warps are the first warps of the CTA");
-    static_assert(split_stage ? ks % issuers == 0 : (a_stages >= issuers && stages >= issuers),
-                  "K blocks dealt out evenly, or rings at least as deep as the number of issuers that stride over them");
+    static_assert(split_stage ? ks % issuers == 0 : (a_stages % issuers == 0 && stages % issuers == 0),
+                  "K blocks dealt out evenly, or ring depths that are multiples of the number of issuers that stride over them");
     static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
     static_assert(acc_col0 + acc_bufs * issuers * acc_stride <= kTmemCols, "tensor memory budget");
     static constexpr int num_barriers = 4 * stages + 2 * a_stages + 2 * acc_bufs;
@@ -385,7 +392,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             const uint32_t row = m_tile * kTileM + row_in_tile;
             // the accumulator holds sum(x * pattern); pattern = code value / 2^bias, so scale by 2^bias * scale[row] here, in fp32
             const float row_scale = __half2float(p.scales[row]) * (float)(1u << (16 - (1 << (E_BITS - 1))));
-            if (!PROF_WAIT(5, ptx::mbar_wait(acc_full, nseg & 1u, abort_word, kErrAccFull, 64))) { ok = false; break; }
+            if (!PROF_WAIT(5, ptx::mbar_wait_warp(acc_full, nseg & 1u, abort_word, kErrAccFull, 64))) { ok = false; break; }
             if (threadIdx.x == 0) PROF_STAMP(7);
             ptx::tc_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::acc_col0;
@@ -478,7 +485,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 const uint32_t in_stage = seg.nkb - sidx * KS;
                 const uint32_t mine = in_stage > kb0 ? (in_stage - kb0 < (uint32_t)KPW ? in_stage - kb0 : (uint32_t)KPW) : 0u;
                 sidx += kStageGroups;
-                if (!PROF_WAIT(0, ptx::mbar_wait(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                if (!PROF_WAIT(0, ptx::mbar_wait_warp(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                 if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == turn) PROF_STAMP(4);
                 PROF_COUNT(6)
                 const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
@@ -512,7 +519,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     }
                     PROF_END(1, t_math)
                     if (!slot_free) {
-                        if (!PROF_WAIT(2, ptx::mbar_wait(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                        if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
                         ptx::tc_fence_after_sync();
                         slot_free = true;
                     }
@@ -523,7 +530,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 PROF_BEGIN(t_st)
                 if (mine == 0) {   // nothing of this stage is ours: still take part in the hand-shakes
                     if (!kUnified && lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);
-                    if (!PROF_WAIT(2, ptx::mbar_wait(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                    if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
                 } else {
                     ptx::tc_wait_st();
                     ptx::tc_fence_before_sync();

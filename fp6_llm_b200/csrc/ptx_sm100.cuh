@@ -70,6 +70,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same wait for a whole warp, leaving it converged and with one verdict.  The lanes poll independently and can
+// leave the loop in different iterations; warp-wide tcgen05 instructions (.sync.aligned loads, stores and waits)
+// that follow a wait must be executed by all lanes together, so the lanes meet again here.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_word, int code,
+                                               uint32_t sleep_ns = 32, uint64_t timeout_ns = 2000000000ull) {
+    const bool ok = mbar_wait(bar, parity, abort_word, code, sleep_ns, timeout_ns);
+    return __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+}
+
 // Position in a ring of SIZE slots: slot index and the parity of the number of completed laps.
 template <int SIZE>
 struct RingPos {
