@@ -39,7 +39,7 @@ WORKLOADS = {
                        [1, 16, 64]),
     "llama2-70b-fp6": (3, 2, [("qkv", 10240, 8192), ("o", 8192, 8192), ("gate_up", 57344, 8192), ("down", 8192, 28672)],
                        [1, 4, 16, 64, 128]),
-    "llama2-70b-prefill-fp6": (3, 2, [("gate_up", 57344, 8192)], [512, 1024, 2048]),
+    "llama2-70b-prefill-fp6": (3, 2, [("gate_up", 57344, 8192), ("down", 8192, 28672)], [512, 1024, 2048]),
     "single-4096-fp6": (3, 2, [("square", 4096, 4096)], [8]),
 }
 DEFAULT_WORKLOAD = "llama2-7b-fp6"
@@ -254,9 +254,7 @@ def run_ours(args):
     # of the stream is still finishing (see fp6b200_set_option in include/fp6_llm_b200.h).
     torch.cuda.synchronize(dev)
     f.set_static_weights(not args.no_static_weights)
-    # With 4 and 8 ranks long chains of one sharded layer ended in a launch failure after the GEMM had been given a
-    # programmatic launch (not explained yet); those runs keep plain stream order in front of every GEMM.
-    f.set_programmatic_launch(not args.no_programmatic_launch and (world < 4 or args.force_programmatic_launch))
+    f.set_programmatic_launch(not args.no_programmatic_launch)
     acts = {(mdl["name"], bs): torch.randn(bs, mdl["ic"], device=dev, dtype=torch.float16) for mdl in models for bs in batches}
     cases = [(mdl, bs) for bs in batches for mdl in models]
     # split_k = 0: the library decomposes the work itself (tile waves + stream-K remainder + fix-up kernel)
@@ -480,7 +478,6 @@ def main():
                     help="N > 1: also time every (layer, batch) pair alone (off by default: the step time is the result)")
     ap.add_argument("--compare-cublas", action="store_true",
                     help="also time torch's fp16 GEMM on GPU-dequantised weights for every case (single GPU)")
-    ap.add_argument("--force-programmatic-launch", action="store_true", help="N >= 4: keep the programmatic launch of the GEMM")
     ap.add_argument("--no-programmatic-launch", action="store_true",
                     help="plain stream order between a GEMM and the kernel before it")
     ap.add_argument("--no-static-weights", action="store_true",

@@ -739,11 +739,9 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    // Not for the 256-wide tile: chains of such launches on a large layer (8192 x 28672, batch 1024) ended in a launch
-    // failure whose cause has not been found; that configuration keeps plain stream order between launches.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = (N_TILE <= 128 && programmatic_launch()) ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = programmatic_launch() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, map, prm);
@@ -907,7 +905,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        const int early = (n_tile <= 128 && programmatic_launch()) ? 1 : 0;   // wide tiles: plain stream order all the way (see launch_one)
+        const int early = programmatic_launch() ? 1 : 0;
         return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan, early);
     }
     if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true);
