@@ -5,16 +5,17 @@
 // warp-specialised kernel built around Blackwell's tensor memory.  One CTA per SM walks a list of
 // segments (output tile 128 x N_TILE, range of 64-wide K blocks; see WorkPlan in fpx_layout.h):
 //
-//   warps 4-5   fill a deep shared-memory ring, one stage = 128 rows x 128 K (64 K for the widest tile):
-//               first the activation tile [N_TILE x 64] per K block with a 2-D TMA tensor copy (128-byte
-//               swizzle, rows past N zero-filled), then the packed weight segments with 1-D bulk copies
-//               (the packed layout keeps all of K contiguous per 64-row block and segment, so no tensor
+//   warps 4-5   fill a shared-memory ring with the packed weight segments, one stage = 128 rows x 256 K (128 K / 64 K
+//               for the 128- / 256-wide tile): warp 4 the tile's first 64-row block, warp 5 the second, 1-D bulk
+//               copies (the packed layout keeps all of K contiguous per 64-row block and segment, so no tensor
 //               map is needed and one copy per segment and row block covers the whole stage);
+//   warp 22     brings the stage's activation tile [N_TILE x 64 per K block] with one 3-D TMA tensor copy (128-byte
+//               swizzle, rows past N and K blocks past K zero-filled) onto a barrier of its own;
 //   warps 6-21  unpack the segments with shift/LOP3/PRMT sequences into fp16 bit patterns (code value / 2^bias,
 //               exact) and write them STRAIGHT INTO TENSOR MEMORY with tcgen05.st.16x128b: the
 //               reference's packed format hands every lane exactly the registers of an m16k16 A
 //               fragment, which is the register pattern of that store, so the dequantised weights
-//               never touch shared memory;
+//               never touch shared memory; the 16 warps work as teams on alternating stages;
 //   warps 0-3   issue tcgen05.mma.kind::f16 with A from tensor memory and B from shared memory, accumulating
 //               fp32 in tensor memory; narrow tiles are issued by up to four warps, each into its own
 //               accumulator, because one thread cannot issue MMAs fast enough for them.  At the end of a
@@ -22,6 +23,11 @@
 //               with tcgen05.ld, add them, multiply by 2^bias * scale[row] in fp32 (the per-row scale is
 //               applied here, once per output, not once per weight: the unpack warps are the bottleneck at
 //               small batch) and store fp16 output or fp32 partials.
+//
+// The kernel is launched programmatically: it starts while the previous kernel of the stream is finishing and every
+// role executes griddepcontrol.wait before it first touches global memory (weights that the caller declared
+// static are requested before that).  Ring depths are multiples of the stride of every role that visits only every
+// n-th stage (see Config).
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records a code in a status word, drains its
 // own copies, frees its tensor memory and returns.
