@@ -45,14 +45,8 @@ namespace fpx {
 
 namespace {
 
-#ifndef FPX_KS_SMALL
-#define FPX_KS_SMALL 4
-#endif
-// K blocks (64 wide) per pipeline stage for a given tile width
-#ifndef FPX_KS_64
-#define FPX_KS_64 4
-#endif
-constexpr int gemm_ks(int n_tile) { return n_tile <= 32 ? FPX_KS_SMALL : (n_tile <= 64 ? FPX_KS_64 : (n_tile <= 128 ? 2 : 1)); }
+// K blocks (64 wide) per shared-memory pipeline stage for a given tile width
+constexpr int gemm_ks(int n_tile) { return n_tile <= 64 ? 4 : (n_tile <= 128 ? 2 : 1); }
 
 constexpr int kTileM = 128;
 constexpr int kAColsPerKBlock = 32;      // 64 fp16 along K per tensor-memory lane
@@ -67,6 +61,16 @@ constexpr int kActProducerWarp = kFirstDequantWarp + kDequantWarps;   // the las
 constexpr int kWarps = kActProducerWarp + 1;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kTmemCols = 512;      // the whole tensor memory: one CTA per SM
+// Sleep between two polls of a barrier (ns).  The copy producers run stages ahead of their consumers and an issuing warp
+// gets a new position only every few hundred nanoseconds; each failed poll costs issue slots the unpack warps need.
+#ifndef FPX_POLL_PRODUCER
+#define FPX_POLL_PRODUCER 200
+#endif
+#ifndef FPX_POLL_ISSUER
+#define FPX_POLL_ISSUER 40
+#endif
+constexpr uint32_t kPollProducer = FPX_POLL_PRODUCER;
+constexpr uint32_t kPollIssuer = FPX_POLL_ISSUER;
 
 // status codes written by a wait that gave up
 enum : int {
@@ -83,60 +87,55 @@ struct RawBlock {
     static constexpr uint32_t bytes128 = 2u * (seg1 + seg2 + seg4);   // 128 rows x 64 K
 };
 
-// A pipeline stage covers KS K blocks (64 wide each) of one 128-row tile:
-//   shared memory  [activations: KS x (N_TILE x 128 B, 128-byte swizzled)]
-//                  [weights, per segment width: row block 0: KS blocks, row block 1: KS blocks]
-//   tensor memory  KS x 32 columns of fp16 weights per stage of the A ring
+// A shared-memory pipeline stage covers KS K blocks (64 wide each) of one 128-row tile:
+//   [activations: KS x (N_TILE x 128 B, 128-byte swizzled)]
+//   [weights, per segment width: row block 0: KS blocks, row block 1: KS blocks]
+// Tensor memory holds a ring of `a_slots` slots of `kpw` K blocks each (32 columns = 64 fp16 along K per K block and
+// lane) and behind it the accumulators of the issuing warps.
+//
+// Positions.  A position is `kpw` consecutive K blocks of a stage: what one unpack warp turns into fp16 per visit and
+// what is handed to an issuing warp at once.  Every stage contributes ks / kpw positions to one running count p
+// (positions past the end of a tile's K range exist too: they take part in the hand-shakes and are unpacked from
+// whatever the stage holds, but get no MMA).  Position p lives in ring slot p % a_slots.  Unpack group g (four warps,
+// one per tensor-memory lane quadrant) takes the positions p = g (mod 4); issuing warp i takes p = i (mod issuers).
 template <int BW, int N_TILE>
 struct Config {
     using Raw = RawBlock<BW>;
     static constexpr int ks = gemm_ks(N_TILE);
-    // Ring depths.  An mbarrier only tells the parity of its phase, so a waiter must know that the phase before the one
-    // it waits for is complete.  A role that visits only every n-th stage (an unpack team, an issuer that takes whole
-    // stages) knows this when it comes back to a slot on the slot's very next use, i.e. when the ring depth is a
-    // multiple of n; the landing of two copies, unlike the completion of MMAs, is not ordered in time.  (With depth 5
-    // and four teams a warp that came back to a slot four uses later took a copy that had not landed yet for done and
-    // unpacked the slot's previous contents.)
-    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : 4) : (N_TILE <= 16 ? 12 : (N_TILE <= 32 ? 10 : (N_TILE <= 64 ? 8 : 4)));
-    static constexpr int a_stages = ks == 4 ? 3 : (N_TILE <= 64 ? 6 : 4);
-    // when the A ring is as deep as the shared-memory ring one commit frees a whole stage
-    static constexpr bool unified = a_stages == stages;
-    // One thread can issue an MMA only every ~60-90 cycles, far more than a narrow MMA needs on the tensor
-    // pipe, so narrow tiles are issued by several warps, each into its own accumulator (summed in the epilogue).
-    // Issuing warps.  Narrow tiles (256-K stages): every issuer visits every stage and takes the K blocks me, me + 4,
-    // ... of it, so a stage's 16 MMAs are issued in a quarter of the time one thread would need and its ring slots come
-    // back that much sooner.  Wider tiles: issuer i takes the stages i, i + issuers, ... whole (measured faster there).
-    static constexpr bool split_stage = ks == 4;
-    static constexpr int issuers = split_stage ? (N_TILE <= 32 ? 4 : 2) : (N_TILE <= 128 ? 2 : 1);
-    static constexpr int slot_commits = split_stage ? issuers : 1;   // commits that free a ring slot
-    static constexpr int acc_bufs = 1;   // the issuing warps also run the epilogue, so one set of accumulators suffices
+    static constexpr int kpw = N_TILE <= 128 ? 2 : 1;
+    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : 4) : 4;
+    static constexpr int a_slots = 256 / (kpw * (int)kAColsPerKBlock);   // 256 columns of fp16 weights: 4 or 8 slots
+    static constexpr int pos_per_stage = ks / kpw;
+    // One thread can issue an MMA only every ~45-130 cycles and the narrow MMAs occupy the tensor pipe for ~40 only,
+    // so narrow tiles are issued by several warps, each into an accumulator of its own (the epilogue adds them up).
+    static constexpr int issuers = N_TILE <= 64 ? 4 : (N_TILE <= 128 ? 2 : 1);
+    static constexpr int stage_step = kDequantGroups / pos_per_stage;   // an unpack group visits every stage_step-th stage
+    static constexpr int issuer_step = issuers > pos_per_stage ? issuers / pos_per_stage : 1;   // same for an issuing warp
+    static constexpr int stage_issuers = issuers < pos_per_stage ? issuers : pos_per_stage;    // issuers that read one stage
+    // An mbarrier wait sees only the parity of the phase, so a waiter must know that the phase BEFORE the one it
+    // waits for is complete: it must meet a barrier again on that barrier's very next use.  Hence every ring depth
+    // is a multiple of the stride of every role that strides over it.  (With a depth of 5 and a stride of 4 a warp
+    // once took a copy that had not landed yet for done and unpacked the slot's previous contents.)
+    static_assert(ks % kpw == 0 && kDequantGroups % pos_per_stage == 0, "positions per stage");
+    static_assert(stages % stage_step == 0, "an unpack group must meet a shared-memory slot again on the slot's next use");
+    static_assert(stages % issuer_step == 0, "an issuing warp must meet a shared-memory slot again on the slot's next use");
+    static_assert(a_slots % kDequantGroups == 0, "a tensor-memory slot is always filled by the same unpack group");
+    static_assert(a_slots % issuers == 0 && (issuers % pos_per_stage == 0 || pos_per_stage % issuers == 0),
+                  "a slot is always consumed by the same issuing warp");
+    static_assert(issuers <= kMaxIssuers, "issuing warps are the first warps of the CTA");
+    static constexpr int readers = 4 * pos_per_stage;   // unpack warps that read a stage's weights
     static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
     static constexpr uint32_t w_off = ks * b_block;
     static constexpr uint32_t off1 = w_off;
     static constexpr uint32_t off2 = off1 + 2u * ks * Raw::seg1;
     static constexpr uint32_t off4 = off2 + 2u * ks * Raw::seg2;
     static constexpr uint32_t stage_bytes = ks * (b_block + Raw::bytes128);
-    static constexpr uint32_t a_cols = ks * kAColsPerKBlock;
-    static constexpr uint32_t acc_col0 = a_stages * a_cols;
+    static constexpr uint32_t slot_cols = kpw * kAColsPerKBlock;
+    static constexpr uint32_t acc_col0 = a_slots * slot_cols;
     static constexpr uint32_t acc_stride = N_TILE < 32 ? 32u : (uint32_t)N_TILE;
-    // Unpack warps: kDequantGroups groups of four warps (one per tensor-memory lane quadrant) form `teams` teams that
-    // take turns on consecutive stages; inside a team every group unpacks kb_per_warp K blocks of the stage.  Two teams
-    // at least, so that one team computes while the other waits for data or a free slot and stores.
-    static constexpr int teams = ks == 1 ? 4 : 2;
-    static constexpr int groups_per_team = kDequantGroups / teams;
-    static constexpr int kb_per_warp = ks / groups_per_team;
-    static_assert(kDequantGroups % teams == 0 && ks % groups_per_team == 0 && kb_per_warp >= 1, "unpack work split");
-    static_assert(stages % teams == 0, "an unpack team must meet a shared-memory slot again on the slot's next use");
-    static constexpr int readers = 4 * groups_per_team;   // unpack warps per stage
-    // An issuer waits on a ring slot only every `issuers` stages.  A parity wait is only meaningful when the
-    // slot's previous phase is already complete, which the issuer knows from its own previous wait as long as
-    // the rings are at least `issuers` deep.
-    static_assert(issuers <= kMaxIssuers, "issuing warps are the first warps of the CTA");
-    static_assert(split_stage ? ks % issuers == 0 : (a_stages % issuers == 0 && stages % issuers == 0),
-                  "K blocks dealt out evenly, or ring depths that are multiples of the number of issuers that stride over them");
     static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
-    static_assert(acc_col0 + acc_bufs * issuers * acc_stride <= kTmemCols, "tensor memory budget");
-    static constexpr int num_barriers = 4 * stages + 2 * a_stages + 2 * acc_bufs;
+    static_assert(acc_col0 + issuers * acc_stride <= kTmemCols, "tensor memory budget");
+    static constexpr int num_barriers = 4 * stages + 2 * a_slots + 2;
     static constexpr uint32_t smem_bytes = stages * stage_bytes + num_barriers * 8u + 32u;
     static_assert(2u * smem_bytes > 228u * 1024u, "two CTAs must never share an SM: each takes all of tensor memory");
     static_assert(smem_bytes <= 227u * 1024u, "shared memory budget");
@@ -172,6 +171,7 @@ struct Params {
     const __half* scales;
     OutTargets out;             // where finished fp16 tiles go (this GPU's buffer, or every rank's)
     uint32_t weights_static;    // the packed weights are not written by earlier work of the stream: read them at once
+    UnpackMul mul[2];           // unpack16_mul's multipliers for h = 0, 1 (parameters so that they stay multiplications)
     float* workspace;
     uint32_t M, N, K;
     WorkPlan plan;
@@ -186,10 +186,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     using Raw = typename Cfg::Raw;
     constexpr int KS = Cfg::ks;
     constexpr int R = Cfg::stages;
-    constexpr int SA = Cfg::a_stages;
-    constexpr int NACC = Cfg::acc_bufs;
+    constexpr int SA = Cfg::a_slots;
     constexpr int NI = Cfg::issuers;
-    constexpr bool kUnified = Cfg::unified;
 
     // 128-byte-swizzled tiles need a 1024-byte aligned base; the dynamic window starts at offset 0 of the
     // CTA's shared memory (no static shared memory in this kernel), which is checked below.
@@ -200,10 +198,10 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     const uint32_t b_full = w_full + 8 * R;              // the stage's activations have landed
     const uint32_t w_empty = b_full + 8 * R;             // the unpack warps have read the weights of the stage
     const uint32_t b_empty = w_empty + 8 * R;            // the MMAs that read the activations of the stage are done
-    const uint32_t a_full = b_empty + 8 * R;
-    const uint32_t a_empty = a_full + 8 * SA;
+    const uint32_t a_full = b_empty + 8 * R;             // per tensor-memory slot: the K block's fp16 weights are stored
+    const uint32_t a_empty = a_full + 8 * SA;            // per slot: the MMAs that read it are done
     const uint32_t acc_full = a_empty + 8 * SA;
-    const uint32_t acc_empty = acc_full + 8 * NACC;
+    const uint32_t acc_empty = acc_full + 8;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_dyn + R * Cfg::stage_bytes + 8 * Cfg::num_barriers);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -220,16 +218,16 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrSmemAlign);
         return;
     }
-    // Set-up.  The first producer warp initialises every barrier; the two producer warps then meet on a barrier of
+    // Set-up.  The first producer warp initialises every barrier; the producer warps then meet on a barrier of
     // their own and start copying at once, while the rest of the CTA waits for the tensor-memory allocation too.
     if (warp == kProducerWarp) {   // one barrier per lane and round
         for (int i = lane; i < R; i += 32) {
             ptx::mbar_init(w_full + 8 * i, kProducerWarps);
             ptx::mbar_init(b_full + 8 * i, 1);
             ptx::mbar_init(w_empty + 8 * i, Cfg::readers);
-            ptx::mbar_init(b_empty + 8 * i, Cfg::slot_commits);
+            ptx::mbar_init(b_empty + 8 * i, Cfg::stage_issuers);
         }
-        for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, Cfg::readers); ptx::mbar_init(a_empty + 8 * i, Cfg::slot_commits); }
+        for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, 4); ptx::mbar_init(a_empty + 8 * i, 1); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
         if (lane == 0) *abort_word = 0;
         ptx::fence_barrier_init();
@@ -267,7 +265,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             const uint8_t* reg2 = p.region[1];
             const uint8_t* reg4 = p.region[2];
             const uint32_t my_full = acts ? b_full : w_full;
-            const uint32_t my_empty = kUnified ? a_empty : (acts ? b_empty : w_empty);
+            const uint32_t my_empty = acts ? b_empty : w_empty;
             bool waited = !acts && p.weights_static != 0;   // nothing to wait for before static weights are read
             ptx::RingPos<R> pos;
             pos.set(0);
@@ -288,7 +286,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     const uint32_t kb_off = sidx * KS;
                     const uint32_t cnt = seg.nkb - kb_off < (uint32_t)KS ? seg.nkb - kb_off : (uint32_t)KS;
                     sidx = sidx + 1 == nstages ? 0u : sidx + 1;
-                    if (!PROF_WAIT(0, ptx::mbar_wait(my_empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty))) { ok = false; break; }
+                    if (!PROF_WAIT(0, ptx::mbar_wait(my_empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, kPollProducer))) { ok = false; break; }
                     PROF_COUNT(6)
                     if (!waited) {
                         asm volatile("griddepcontrol.wait;" ::: "memory");   // first read of memory the previous kernel may write
@@ -319,15 +317,16 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
                 const uint32_t first = issued > (uint32_t)R ? issued - R : 0u;
                 for (uint32_t t = first; t < issued; t++)
-                    ptx::mbar_wait(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, 64, 50000000ull);
+                    ptx::mbar_wait(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, kPollProducer, 50000000ull);
             }
         }
         __syncwarp();
     } else if (warp < kMaxIssuers) {
         // ------------------------------------------------------------ MMA issue + epilogue
         // Per segment: lane 0 of the first NI warps issues the MMAs (issuer i takes the K blocks i, i + NI, ... of every
-        // stage and accumulates them in its own accumulator); then all four warps, one per tensor-memory lane quadrant,
-        // read the accumulators, add them and store the tile (lane = output channel, column = token).
+        // stage, each as soon as its slot of the tensor-memory ring is full, and accumulates them in its own
+        // accumulator); then all four warps, one per tensor-memory lane quadrant, read the accumulators, add them and
+        // store the tile (lane = output channel, column = token).
         constexpr uint32_t idesc = ptx::idesc_f16_f32(kTileM, N_TILE);
         const uint32_t me = (uint32_t)warp;
         const int q = warp & 3;
@@ -342,55 +341,80 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         while (ok && plan_next(plan, cta, &iter, &seg)) {
             const uint32_t nstages = (seg.nkb + KS - 1) / KS;
             if (me < (uint32_t)NI && lane == 0) {
-                if (!PROF_WAIT(2, ptx::mbar_wait(acc_empty, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty, 64))) ok = false;
+                if (!PROF_WAIT(2, ptx::mbar_wait(acc_empty, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty))) ok = false;
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + Cfg::acc_col0 + me * Cfg::acc_stride;
+                constexpr uint32_t PPS = (uint32_t)Cfg::pos_per_stage, IST = (uint32_t)Cfg::issuer_step, KPW = (uint32_t)Cfg::kpw;
+                // positions p = me (mod NI): K blocks [sub * KPW, (sub + 1) * KPW) of the stages j = first (mod IST)
+                const uint32_t sub0 = me % PPS;                                  // first position of mine inside a stage
+                const uint32_t cls_i = (me / PPS) % IST;
+                uint32_t t = (cls_i + IST - (j0 % IST)) % IST;                    // my first stage of the segment
                 ptx::RingPos<R> rp;
                 ptx::RingPos<SA> ap;
-                constexpr uint32_t kStep = Cfg::split_stage ? 1u : (uint32_t)NI;   // stages between two visits of this issuer
-                const uint32_t t0 = Cfg::split_stage ? 0u : me;
-                rp.set(j0 + t0);
-                ap.set(j0 + t0);
-                uint32_t sidx = plan_first_stage(cta, nstages) + t0;          // stage of the segment's K range handled next
-                uint32_t accumulate = 0u;                                    // 0 only for this issuer's first MMA of the segment
-                for (uint32_t t = t0; ok && t < nstages; t += kStep) {
+                rp.set(j0 + t);
+                ap.set((j0 + t) * PPS + sub0);
+                uint32_t sidx = plan_first_stage(cta, nstages) + t;              // stage of the segment's K range handled next
+                uint32_t accumulate = 0u;                                        // 0 only for this issuer's first MMA of the segment
+                for (; ok && t < nstages; t += IST) {
                     while (sidx >= nstages) sidx -= nstages;
                     const uint32_t cnt = seg.nkb - sidx * KS < (uint32_t)KS ? seg.nkb - sidx * KS : (uint32_t)KS;
-                    sidx += kStep;
-                    if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull))) { ok = false; break; }
-                    if (me == 0 && nseg == 0 && t == t0) PROF_STAMP(5);
-                    // the activations of the stage landed before its weights were unpacked; this only makes them visible here
+                    sidx += IST;
                     if (!PROF_WAIT(1, ptx::mbar_wait(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
-                    PROF_BEGIN(t_issue)
-                    ptx::tc_fence_after_sync();
                     const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::stage_bytes >> 4));
-                    const uint32_t a_tmem = tmem_base + ap.idx * Cfg::a_cols;
-#if !(defined(FPX_EXP) && (FPX_EXP & 4))
 #pragma unroll
-                    for (uint32_t kbi = Cfg::split_stage ? me : 0u; kbi < (uint32_t)KS; kbi += Cfg::split_stage ? (uint32_t)NI : 1u)
-                        if (kbi < cnt) {
+                    for (uint32_t sub = sub0; sub < PPS; sub += (uint32_t)NI) {
+                        if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull, kPollIssuer))) { ok = false; break; }
+                        if (me == 0 && nseg == 0 && t == 0) PROF_STAMP(5);
+                        PROF_BEGIN(t_issue)
+                        ptx::tc_fence_after_sync();
+                        const uint32_t a_tmem = tmem_base + ap.idx * Cfg::slot_cols;
 #pragma unroll
-                            for (uint32_t kk = 0; kk < 4; kk++) {   // four K=16 steps; B advances 32 bytes inside the swizzle row
-                                ptx::mma_f16_ts(d_tmem, a_tmem + kbi * kAColsPerKBlock + kk * 8,
-                                                b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
-                                accumulate = 1u;
+                        for (uint32_t b = 0; b < KPW; b++) {
+                            const uint32_t kbi = sub * KPW + b;
+                            if (kbi < cnt) {
+#pragma unroll
+                                for (uint32_t kk = 0; kk < 4; kk++) {   // four K=16 steps; B advances 32 bytes inside the swizzle row
+                                    ptx::mma_f16_ts(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
+                                                    b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
+                                    accumulate = 1u;
+                                }
                             }
                         }
-#endif
-                    PROF_END(3, t_issue)
-                    PROF_BEGIN(t_commit)
-                    ptx::tc_commit(a_empty + 8 * ap.idx);
-                    if (!kUnified) ptx::tc_commit(b_empty + 8 * rp.idx);
-                    PROF_END(4, t_commit)
+                        PROF_END(3, t_issue)
+                        PROF_BEGIN(t_commit)
+                        ptx::tc_commit(a_empty + 8 * ap.idx);
+                        PROF_END(4, t_commit)
+                        ap.advance(NI);
+                    }
+                    if (!ok) break;
+                    ptx::tc_commit(b_empty + 8 * rp.idx);
                     if (me == 0) PROF_STAMP(6);
-                    rp.advance(kStep);
-                    ap.advance(kStep);
+                    rp.advance(IST);
                 }
                 if (ok) ptx::tc_commit(acc_full);   // arrives once this issuer's MMAs (if any) are done
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
+            // Which issuers hold a sum for this segment: issuer i visited the stages t = t_first (mod issuer_step); with two
+            // or more visits one of them was a full stage, with one visit its first position must hold a K block.
+            uint32_t has_data = 0;
+            {
+                constexpr uint32_t PPS = (uint32_t)Cfg::pos_per_stage, IST = (uint32_t)Cfg::issuer_step;
+                const uint32_t first_stage = plan_first_stage(cta, nstages);
+#pragma unroll
+                for (uint32_t i = 0; i < (uint32_t)NI; i++) {
+                    const uint32_t t_first = ((i / PPS) % IST + IST - (j0 % IST)) % IST;
+                    bool has = t_first < nstages;
+                    if (has && t_first + IST >= nstages) {
+                        uint32_t only = first_stage + t_first;
+                        if (only >= nstages) only -= nstages;
+                        const uint32_t cnt = seg.nkb - only * KS;   // >= KS for every stage but the last of the K range
+                        has = (i % PPS) * (uint32_t)Cfg::kpw < cnt;
+                    }
+                    has_data |= (has ? 1u : 0u) << i;
+                }
+            }
             j0 += nstages;
 
             const uint32_t m_tile = plan.n_tiles == 1 ? seg.tile : seg.tile / plan.n_tiles, n_tile = seg.tile - m_tile * plan.n_tiles;
@@ -398,14 +422,11 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             const uint32_t row = m_tile * kTileM + row_in_tile;
             // the accumulator holds sum(x * pattern); pattern = code value / 2^bias, so scale by 2^bias * scale[row] here, in fp32
             const float row_scale = __half2float(p.scales[row]) * (float)(1u << (16 - (1 << (E_BITS - 1))));
-            if (!PROF_WAIT(5, ptx::mbar_wait_warp(acc_full, nseg & 1u, abort_word, kErrAccFull, 64))) { ok = false; break; }
+            if (!PROF_WAIT(5, ptx::mbar_wait_warp(acc_full, nseg & 1u, abort_word, kErrAccFull))) { ok = false; break; }
             if (threadIdx.x == 0) PROF_STAMP(7);
             ptx::tc_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::acc_col0;
-            // issuers that contributed: the fullest stage of the segment holds min(KS, nkb) K blocks (dealt to the issuers),
-            // or, when the issuers take whole stages, one issuer per stage
-            const uint32_t have = Cfg::split_stage ? seg.nkb : nstages;
-            const uint32_t parts = have < (uint32_t)NI ? have : (uint32_t)NI;
+            // issuers that contributed: the fullest stage of the segment holds min(KS, nkb) K blocks, dealt to the issuers in turn
             constexpr int CH = 16;   // columns handled per round
 #pragma unroll 1
             for (int c0 = 0; c0 < N_TILE; c0 += CH) {
@@ -413,13 +434,11 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 if (n0 >= p.N) break;
                 uint32_t v[CH];
                 float f[CH];
-                ptx::tmem_ld_cols<CH>(acc + c0, v);
-                ptx::tc_wait_ld();
 #pragma unroll
-                for (int u = 0; u < CH; u++) f[u] = __uint_as_float(v[u]);
+                for (int u = 0; u < CH; u++) f[u] = 0.0f;
 #pragma unroll
-                for (uint32_t i = 1; i < (uint32_t)NI; i++)
-                    if (i < parts) {
+                for (uint32_t i = 0; i < (uint32_t)NI; i++)
+                    if ((has_data >> i) & 1u) {
                         ptx::tmem_ld_cols<CH>(acc + i * Cfg::acc_stride + c0, v);
                         ptx::tc_wait_ld();
 #pragma unroll
@@ -450,102 +469,114 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(acc_empty);
+            ptx::mbar_arrive_elected(acc_empty);
             if (threadIdx.x == 0) PROF_STAMP(8);
             nseg++;
         }
         PROF_FLUSH();
     } else if (warp >= kFirstDequantWarp && warp < kActProducerWarp) {
         // ------------------------------------------------------------ unpack warps
+        // Group g (four warps, one per lane quadrant) takes the K-block positions c = g (mod 4) of the CTA's running
+        // count: K block g % KS of every stage_step-th stage.  Per position: wait for the stage's weights, read the
+        // lane's words, hand the shared-memory stage back, unpack, wait for the position's tensor-memory slot, store,
+        // tell the issuing warp.
         const int q = warp & 3;                                   // tensor-memory lane quadrant this warp may touch
         const uint32_t group = (uint32_t)(warp - kFirstDequantWarp) >> 2;
-        constexpr uint32_t kStageGroups = Cfg::teams;             // teams take turns on consecutive stages
-        constexpr int KPW = Cfg::kb_per_warp;                     // K blocks of a stage this warp unpacks
-        const uint32_t turn = group % kStageGroups;               // it takes the stages j with j % kStageGroups == turn
-        const uint32_t kb0 = (group / kStageGroups) * KPW;        // its first K block inside a stage
+        constexpr uint32_t ST = Cfg::stage_step, PPS = Cfg::pos_per_stage;
+        constexpr int KPW = Cfg::kpw;
+        const uint32_t cls = (group / PPS) % ST;                  // it takes the stages j with j % ST == cls
+        const uint32_t kb0 = (group % PPS) * KPW;                 // and these K blocks of them
         const int h = q & 1;                                      // sub-blocks 2h, 2h+1 of the 64-row block
         const int rb = q >> 1;                                    // 64-row block inside the 128-row tile
         const uint32_t lane_base = ring + 4u * lane;
         const uint32_t o4 = Cfg::off4 + (rb * KS + kb0) * Raw::seg4 + 2 * h * 128;
         const uint32_t o2 = Cfg::off2 + (rb * KS + kb0) * Raw::seg2 + h * 128;
         const uint32_t o1 = Cfg::off1 + (rb * KS + kb0) * Raw::seg1;
-        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * q) << 16) + kb0 * kAColsPerKBlock;
-        uint32_t j0 = 0;   // running stage index at the start of the segment
+        const uint32_t a_lane = tmem_base + ((uint32_t)(32 * q) << 16);
+        const UnpackMul km = p.mul[h];
+        // Per visit: wait for the stage's weights, then K block by K block read the lane's words, unpack them and store
+        // the fp16 patterns into the position's tensor-memory slot (the words of the next K block are requested before
+        // the stores of this one go out); hand the shared-memory stage back as soon as the last words are read, and the
+        // slot to the issuing warp once the stores have completed.  (Handing the slot over only at the start of the
+        // next visit, to hide the wait for the stores, measured 6 % slower: the MMAs then finish too late for the
+        // group's next visit, which needs the same slot.)  Positions past the end of a K range are unpacked like any
+        // other (from whatever the stage holds): they get no MMA.
+        uint32_t j0 = 0;            // running stage index at the start of the segment
+        uint32_t slot = 0, slot_lap = 0, slot_primed = 0;
+        uint32_t pending_bar = 0;   // a_full barrier of the position whose stores are in flight
         bool ok = true;
         SegmentIter iter;
         Segment seg;
         PROF_DECL
         plan_start(plan, cta, &iter);
+        uint32_t w4[4][2], w2[4], w1[4];
+        auto load_words = [&](uint32_t raw, int b) {
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                w4[jj][0] = ptx::lds_u32(raw + o4 + b * Raw::seg4 + (jj * 4 + 0) * 128);
+                w4[jj][1] = ptx::lds_u32(raw + o4 + b * Raw::seg4 + (jj * 4 + 1) * 128);
+                w2[jj] = Raw::seg2 ? ptx::lds_u32(raw + o2 + b * Raw::seg2 + (jj * 2) * 128) : 0u;
+                w1[jj] = Raw::seg1 ? ptx::lds_u32(raw + o1 + b * Raw::seg1 + jj * 128) : 0u;
+            }
+        };
+        // the stores of a position have completed: tell the issuing warp
+        auto hand_over = [&]() {
+            ptx::tc_wait_st();
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            ptx::mbar_arrive_elected(pending_bar);
+            pending_bar = 0;
+        };
         while (ok && plan_next(plan, cta, &iter, &seg)) {
             const uint32_t nstages = (seg.nkb + KS - 1) / KS;
-            // this warp's first stage of the segment
-            uint32_t t = (turn + kStageGroups - (j0 % kStageGroups)) % kStageGroups;
+            uint32_t t = (cls + ST - (j0 % ST)) % ST;     // this group's first stage of the segment
             ptx::RingPos<R> rp;
-            ptx::RingPos<SA> ap;
             rp.set(j0 + t);
-            ap.set(j0 + t);
-            uint32_t sidx = plan_first_stage(cta, nstages) + t;   // stage of the segment's K range handled next
-            for (; t < nstages; t += kStageGroups) {
-                while (sidx >= nstages) sidx -= nstages;
-                // K blocks of this stage that exist for this warp (the last stage of the K range may hold fewer)
-                const uint32_t in_stage = seg.nkb - sidx * KS;
-                const uint32_t mine = in_stage > kb0 ? (in_stage - kb0 < (uint32_t)KPW ? in_stage - kb0 : (uint32_t)KPW) : 0u;
-                sidx += kStageGroups;
+            if (!slot_primed && t < nstages) {            // the group's first position of all: p = (j0 + t) * PPS + group % PPS
+                ptx::RingPos<SA> ap;
+                ap.set((j0 + t) * PPS + group % PPS);
+                slot = ap.idx; slot_lap = ap.lap; slot_primed = 1;
+            }
+            for (; t < nstages; t += ST) {
                 if (!PROF_WAIT(0, ptx::mbar_wait_warp(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
-                if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == turn) PROF_STAMP(4);
+                if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == cls) PROF_STAMP(4);
                 PROF_COUNT(6)
                 const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
-                const uint32_t a_addr = a_lane + ap.idx * Cfg::a_cols;
-                bool slot_free = false;
+                load_words(raw, 0);
+                const uint32_t a_addr = a_lane + slot * Cfg::slot_cols;
 #pragma unroll
                 for (int b = 0; b < KPW; b++) {
-                    if ((uint32_t)b >= mine) break;
                     PROF_BEGIN(t_math)
                     uint32_t v[2][16];
-                    uint32_t w4[4][2], w2[4], w1[4];
-#pragma unroll
-                    for (int jj = 0; jj < 4; jj++) {
-                        w4[jj][0] = ptx::lds_u32(raw + o4 + b * Raw::seg4 + (jj * 4 + 0) * 128);
-                        w4[jj][1] = ptx::lds_u32(raw + o4 + b * Raw::seg4 + (jj * 4 + 1) * 128);
-                        w2[jj] = Raw::seg2 ? ptx::lds_u32(raw + o2 + b * Raw::seg2 + (jj * 2) * 128) : 0u;
-                        w1[jj] = Raw::seg1 ? ptx::lds_u32(raw + o1 + b * Raw::seg1 + jj * 128) : 0u;
-                    }
-                    if (!kUnified && (uint32_t)b + 1 == mine) {
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);   // the weights can be refilled while we compute
-                    }
 #pragma unroll
                     for (int jj = 0; jj < 4; jj++) {
                         uint32_t pat[8];
-                        unpack16<E_BITS>(w4[jj][0], w4[jj][1], w2[jj], w1[jj], h, pat);
+                        unpack16_mul<E_BITS>(w4[jj][0], w4[jj][1], w2[jj], w1[jj], km, pat);
 #pragma unroll
                         for (int kk = 0; kk < 2; kk++)
 #pragma unroll
                             for (int i = 0; i < 4; i++) v[kk][4 * jj + i] = pat[4 * kk + i];
                     }
                     PROF_END(1, t_math)
-                    if (!slot_free) {
-                        if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                    if (b + 1 < KPW) {
+                        load_words(raw, b + 1);
+                    } else {
+                        __syncwarp();
+                        ptx::mbar_arrive_elected(w_empty + 8 * rp.idx);   // the weights can be refilled
+                    }
+                    if (b == 0) {
+                        if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * slot, slot_lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
                         ptx::tc_fence_after_sync();
-                        slot_free = true;
                     }
                     ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock, v[0]);
                     ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock + (16u << 16), v[1]);
                 }
                 if (!ok) break;
-                PROF_BEGIN(t_st)
-                if (mine == 0) {   // nothing of this stage is ours: still take part in the hand-shakes
-                    if (!kUnified && lane == 0) ptx::mbar_arrive(w_empty + 8 * rp.idx);
-                    if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * ap.idx, ap.lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
-                } else {
-                    ptx::tc_wait_st();
-                    ptx::tc_fence_before_sync();
-                }
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(a_full + 8 * ap.idx);
-                PROF_END(3, t_st)
-                rp.advance(kStageGroups);
-                ap.advance(kStageGroups);
+                pending_bar = a_full + 8 * slot;
+                hand_over();
+                slot += kDequantGroups;
+                if (slot >= (uint32_t)SA) { slot -= SA; slot_lap ^= 1u; }
+                rp.advance(ST);
             }
             j0 += nstages;
         }
@@ -864,6 +895,8 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     prm.out = where;
     prm.workspace = workspace;
     prm.weights_static = (uint32_t)weights_static();
+    prm.mul[0] = unpack_mul_values(0);
+    prm.mul[1] = unpack_mul_values(1);
     prm.M = (uint32_t)M;
     prm.N = (uint32_t)N;
     prm.K = (uint32_t)K;

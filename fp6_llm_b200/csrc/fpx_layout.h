@@ -148,6 +148,62 @@ FPX_HD void unpack16(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, int h
     out[4] = expand_13(y2); out[5] = expand_02(y2); out[6] = expand_13(y3); out[7] = expand_02(y3);
 }
 
+// The same unpack for the GEMM's inner loop, in fewer instructions and with part of them moved off the logic pipe.
+// On B200 the logic operations (LOP3, PRMT, funnel shifts) issue at 64 lanes per clock and SM, and integer
+// multiply-adds issue at the same rate on the other (FMA) pipe; the sequence above keeps only the logic pipe busy.
+// Here the sign and exponent bits are brought into one word once, the left shifts are multiplications, and the low
+// nibbles are what is left of the word after the high ones (w - 16 * high).  The multipliers come in through `k`
+// (kernel parameters on the device), so that the compiler cannot turn them back into shifts; the values are fixed:
+//   m4 = 4, m16 = 16, mneg16 = -16, sign[i] = 1 << (4h + i)  (e2m2 only; h as above).
+struct UnpackMul {
+    uint32_t m4, m16, mneg16;
+    uint32_t sign[4];
+};
+FPX_HD UnpackMul unpack_mul_values(int h) {
+    UnpackMul k;
+    k.m4 = 4u; k.m16 = 16u; k.mneg16 = 0u - 16u;
+    for (int i = 0; i < 4; i++) k.sign[i] = 1u << (4 * h + i);
+    return k;
+}
+FPX_HD uint32_t mul_add(uint32_t a, uint32_t b, uint32_t c) {
+#if defined(__CUDA_ARCH__)
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+#else
+    return a * b + c;
+#endif
+}
+FPX_HD uint32_t rot_left(uint32_t x, int n) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_l(x, x, n);
+#else
+    return (x << n) | (x >> (32 - n));
+#endif
+}
+template <int E_BITS>
+FPX_HD void unpack16_mul(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, const UnpackMul& k, uint32_t out[8]) {
+    const uint32_t nib0 = (w4a >> 4) & 0x0f0f0f0fu, nib2 = (w4b >> 4) & 0x0f0f0f0fu;
+    const uint32_t nib1 = mul_add(nib0, k.mneg16, w4a), nib3 = mul_add(nib2, k.mneg16, w4b);
+    uint32_t y[4];
+    if (E_BITS == 3) {
+        // se: the sign of iteration n' at bit 7-2n' and its e2 three bits below (at bit 4-2n'; for n' = 3 that is bit 6 of
+        // the byte below, and of the top byte for the lowest one), so one shift or rotation by 2n' puts both in place
+        const uint32_t se = (w2 & 0xaaaaaaaau) | rot_left(w2 & 0x55555555u, 30);
+        y[0] = (se & 0x90909090u) | nib0;
+        y[1] = (mul_add(se, k.m4, 0u) & 0x90909090u) | nib1;
+        y[2] = (mul_add(se, k.m16, 0u) & 0x90909090u) | nib2;
+        y[3] = (rot_left(se, 6) & 0x90909090u) | nib3;
+    } else {
+        y[0] = (mul_add(w1, k.sign[0], 0u) & 0x80808080u) | nib0;
+        y[1] = (mul_add(w1, k.sign[1], 0u) & 0x80808080u) | nib1;
+        y[2] = (mul_add(w1, k.sign[2], 0u) & 0x80808080u) | nib2;
+        y[3] = (mul_add(w1, k.sign[3], 0u) & 0x80808080u) | nib3;
+    }
+    out[0] = expand_13(y[0]); out[1] = expand_02(y[0]); out[2] = expand_13(y[1]); out[3] = expand_02(y[1]);
+    out[4] = expand_13(y[2]); out[5] = expand_02(y[2]); out[6] = expand_13(y[3]); out[7] = expand_02(y[3]);
+}
+
 // Round-to-nearest quantiser (2 mantissa bits).  Value of the non-negative code c: subnormals m/4 * 2^(1-bias),
 // otherwise (1 + m/4) * 2^(e-bias), bias = 2^(E-1) - 1 (28 is the largest e3m2 magnitude, 7 the largest e2m2 one).
 FPX_HD float fpx_magnitude(int e_bits, int c) {

@@ -45,38 +45,78 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Polls the barrier inside one instruction sequence, without a branch the compiler has to reconverge: up to `tries`
+// tests with a sleep of `sleep_ns` after each failed one.  A sleeping thread issues nothing, and every failed test costs
+// five instructions, so roles that are far ahead of their partner (the copy producers) sleep long and only a role on
+// the critical path polls quickly.
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, uint32_t tries, uint32_t sleep_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n"
+        "FPX_SPIN:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra FPX_DONE;\n\t"
+        "nanosleep.u32 %3;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 p, n, %4;\n\t"
+        "@p bra FPX_SPIN;\n\t"
+        "setp.ne.u32 p, n, n;\n"
+        "FPX_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(sleep_ns), "r"(tries)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Returns false when the CTA-wide abort word is (or becomes) non-zero: either another
 // thread gave up, or this wait itself ran past `timeout_ns`, in which case it records `code` there.
-// Between polls the thread sleeps `sleep_ns` so that waiting warps do not flood the shared-memory pipe
-// that the copy and MMA issuing threads also need; the clock is only consulted every 256 polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int code,
-                                          uint32_t sleep_ns = 32, uint64_t timeout_ns = 2000000000ull) {
-    if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = 0;
-    uint32_t spins = 0;
-#pragma unroll 1
+// The clock and the abort word are only looked at between rounds of 1024 polls.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_word, int code, uint32_t sleep_ns,
+                                            uint64_t timeout_ns) {
+    const uint64_t t0 = global_timer_ns();
     for (;;) {
-        __nanosleep(sleep_ns);
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 255u) == 0u) {
-            if (*abort_word != 0) return false;
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > timeout_ns) {
-                *abort_word = code;
-                return false;
-            }
+        if (mbar_spin(bar, parity, 1024u, sleep_ns)) return true;
+        if (*abort_word != 0) return false;
+        if (global_timer_ns() - t0 > timeout_ns) {
+            *abort_word = code;
+            return false;
         }
     }
 }
+constexpr uint32_t kPollFast = 20;   // ns between polls of a role on the critical path
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int code,
+                                          uint32_t sleep_ns = kPollFast, uint64_t timeout_ns = 2000000000ull) {
+    if (mbar_spin(bar, parity, 1024u, sleep_ns)) return true;
+    return mbar_wait_slow(bar, parity, abort_word, code, sleep_ns, timeout_ns);
+}
 
 // The same wait for a whole warp, leaving it converged and with one verdict.  The lanes poll independently and can
-// leave the loop in different iterations; warp-wide tcgen05 instructions (.sync.aligned loads, stores and waits)
+// leave the loop in different rounds; warp-wide tcgen05 instructions (.sync.aligned loads, stores and waits)
 // that follow a wait must be executed by all lanes together, so the lanes meet again here.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_word, int code,
-                                               uint32_t sleep_ns = 32, uint64_t timeout_ns = 2000000000ull) {
-    const bool ok = mbar_wait(bar, parity, abort_word, code, sleep_ns, timeout_ns);
-    return __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+                                               uint32_t sleep_ns = kPollFast, uint64_t timeout_ns = 2000000000ull) {
+    bool ok = mbar_spin(bar, parity, 1024u, sleep_ns);
+    if (!__all_sync(0xffffffffu, ok ? 1 : 0)) {
+        if (!ok) ok = mbar_wait_slow(bar, parity, abort_word, code, sleep_ns, timeout_ns);
+        ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+    }
+    return ok;
+}
+
+// One lane of the (converged) warp arrives for all of it.
+__device__ __forceinline__ void mbar_arrive_elected(uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t"
+        "}\n" ::"r"(bar)
+        : "memory");
 }
 
 // Position in a ring of SIZE slots: slot index and the parity of the number of completed laps.
@@ -94,11 +134,6 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t smem_addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr));
     return v;
-}
-
-// ------------------------------------------------------------------ proxies / fences
-__device__ __forceinline__ void fence_proxy_async_smem() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // ------------------------------------------------------------------ L2 policies
@@ -122,16 +157,7 @@ __device__ __forceinline__ void bulk_g2s(uint32_t smem_dst, const void* gmem_src
         ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar), "l"(policy)
         : "memory");
 }
-// 2-D tiled tensor copy global -> shared through a tensor map.  x is the innermost coordinate.
-__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
-                                            uint32_t bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%2, %3}], [%4], %5;"
-        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
-        : "memory");
-}
-// 3-D variant; x is the innermost coordinate.
+// 3-D tiled tensor copy global -> shared through a tensor map; x is the innermost coordinate.
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
                                             uint32_t bar, uint64_t policy) {
     asm volatile(
@@ -180,18 +206,6 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// D[tmem] (+)= A[smem descriptor] * B[smem descriptor].
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
 // Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows of
 // 128 bytes (64 fp16), 8-row groups 1024 bytes apart, tile base 1024-byte aligned.
 __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
@@ -225,13 +239,7 @@ __device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_
         "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
-// One warp loads, for its 32 TMEM lanes (thread i <-> lane base+i), 8 consecutive 32-bit columns.
-__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&v)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(taddr)
-                 : "memory");
-}
+// One warp loads, for its 32 TMEM lanes (thread i <-> lane base+i), 16 consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
@@ -242,23 +250,11 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)
         : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-// CH = 16 or 32 consecutive columns for the warp's 32 lanes.
+// CH consecutive columns for the warp's 32 lanes.
 template <int CH>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[CH]) {
-    static_assert(CH == 16 || CH == 32, "chunk width");
-    if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr, v);
-    else tmem_ld_32x32b_x32(taddr, v);
+    static_assert(CH == 16, "chunk width");
+    tmem_ld_32x32b_x16(taddr, v);
 }
 
 }  // namespace ptx

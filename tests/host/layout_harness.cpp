@@ -58,6 +58,11 @@ int harness_unpack(int e_bits, int m_bits, uint16_t* out_bits, const uint8_t* pa
                         uint32_t w1 = has_seg(bw, 1) ? r1[j * 32 + lane] : 0u;
                         uint32_t pat[8];
                         if (e_bits == 3) unpack16<3>(w4a, w4b, w2, w1, h, pat); else unpack16<2>(w4a, w4b, w2, w1, h, pat);
+                        // the multiply-based sequence of the GEMM's inner loop must give the same registers
+                        uint32_t pat2[8];
+                        const UnpackMul km = unpack_mul_values(h);
+                        if (e_bits == 3) unpack16_mul<3>(w4a, w4b, w2, w1, km, pat2); else unpack16_mul<2>(w4a, w4b, w2, w1, km, pat2);
+                        for (int i = 0; i < 8; i++) if (pat[i] != pat2[i]) return -2;
                         for (int kk = 0; kk < 2; kk++)
                             for (int i = 0; i < 4; i++) v[kk][4 * j + i] = pat[4 * kk + i];
                     }
