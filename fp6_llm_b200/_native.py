@@ -28,7 +28,15 @@ C_SYMBOLS = (
     "fp6b200_dequant", "fp6b200_dequant_host", "fp6b200_dequant_packed", "fp6b200_splitk_reduce",
     "fp6b200_device_status", "fp6b200_linear_static_scratch", "fp6b200_static_scratch_bytes",
     "fp6b200_linear_gather", "fp6b200_set_option", "fp6b200_get_option", "fp6b200_quantize_prepack",
+    "fp6b200_linear_host_io_batch", "fp6b200_kernel_launches",
 )
+
+
+class HostCall(ctypes.Structure):
+    """fp6b200_host_call of include/fp6_llm_b200.h."""
+    _fields_ = [("e_bits", ctypes.c_int), ("m_bits", ctypes.c_int), ("weight_packed_dev", ctypes.c_void_p),
+                ("scales_dev", ctypes.c_void_p), ("act_host", ctypes.c_void_p), ("out_host", ctypes.c_void_p),
+                ("M", ctypes.c_size_t), ("N", ctypes.c_size_t), ("K", ctypes.c_size_t), ("split_k", ctypes.c_int)]
 
 
 def _nvcc() -> str:
@@ -84,6 +92,10 @@ def lib() -> ctypes.CDLL:
     L.fp6b200_linear.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, ci]
     L.fp6b200_linear_host_io.restype = ci
     L.fp6b200_linear_host_io.argtypes = [ci, ci, vp, vp, vp, vp, sz, sz, sz, ci]
+    L.fp6b200_linear_host_io_batch.restype = ci
+    L.fp6b200_linear_host_io_batch.argtypes = [ctypes.POINTER(HostCall), ci]
+    L.fp6b200_kernel_launches.restype = ci
+    L.fp6b200_kernel_launches.argtypes = [sz, sz, sz, ci]
     L.fp6b200_workspace_bytes.restype = sz
     L.fp6b200_workspace_bytes.argtypes = [sz, sz, sz, ci]
     L.fp6b200_choose_split_k.restype = ci

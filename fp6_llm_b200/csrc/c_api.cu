@@ -5,6 +5,7 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -100,7 +101,7 @@ int* gemm_status_word() { return status_ptr(); }
 
 extern "C" {
 
-int fp6b200_version(void) { return 1; }
+int fp6b200_version(void) { return 2; }
 
 const char* fp6b200_error_string(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }
 
@@ -124,6 +125,8 @@ size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k) {
     if (split_k == 0) return fpx::gemm_auto_workspace_bytes(N);
     return split_k > 1 ? (size_t)split_k * M * N * sizeof(float) : 0;
 }
+
+int fp6b200_kernel_launches(size_t M, size_t N, size_t K, int split_k) { return fpx::gemm_kernel_launches(M, N, K, split_k); }
 
 int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,
                    const void* act, void* out, size_t M, size_t N, size_t K, float* workspace, int split_k) {
@@ -186,6 +189,86 @@ int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev
     err = cudaMemcpyAsync(out_host, out, N * M * sizeof(__half), cudaMemcpyDeviceToHost, stream);
     if (err != cudaSuccess) return err;
     return cudaStreamSynchronize(stream);
+}
+
+// Several layers with host activations/outputs as one pipelined batch: call i+1's activations travel to the device
+// and call i-1's result travels back while call i computes.  Three streams (copy in, compute, copy out) chained by
+// events, one cudaMemcpyAsync per copy, one synchronisation at the end.
+namespace {
+struct BatchContext {
+    cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
+    cudaEvent_t* events = nullptr;
+    int n_events = 0;
+};
+BatchContext g_batch[kMaxDevices];
+
+cudaError_t batch_context(int n_calls, BatchContext** ctx) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    BatchContext& c = g_batch[dev];
+    if (!c.in) {
+        if ((err = cudaStreamCreateWithFlags(&c.in, cudaStreamNonBlocking)) != cudaSuccess) return err;
+        if ((err = cudaStreamCreateWithFlags(&c.compute, cudaStreamNonBlocking)) != cudaSuccess) return err;
+        if ((err = cudaStreamCreateWithFlags(&c.out, cudaStreamNonBlocking)) != cudaSuccess) return err;
+    }
+    if (c.n_events < 2 * n_calls) {
+        cudaEvent_t* grown = static_cast<cudaEvent_t*>(realloc(c.events, sizeof(cudaEvent_t) * 2 * (size_t)n_calls));
+        if (!grown) return cudaErrorMemoryAllocation;
+        c.events = grown;
+        for (int i = c.n_events; i < 2 * n_calls; i++) {
+            if ((err = cudaEventCreateWithFlags(&c.events[i], cudaEventDisableTiming)) != cudaSuccess) return err;
+            c.n_events = i + 1;
+        }
+    }
+    *ctx = &c;
+    return cudaSuccess;
+}
+}  // namespace
+
+int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls) {
+    if (!calls || n_calls <= 0) return cudaErrorInvalidValue;
+    size_t total = 0, ws_bytes = 0;
+    for (int i = 0; i < n_calls; i++) {
+        const fp6b200_host_call& c = calls[i];
+        if (!c.act_host || !c.out_host || !c.weight_packed_dev || !c.scales_dev || c.split_k < 0) return cudaErrorInvalidValue;
+        total += align_up(c.N * c.K * sizeof(__half), 256) + align_up(c.N * c.M * sizeof(__half), 256);
+        const size_t ws = fp6b200_workspace_bytes(c.M, c.N, c.K, c.split_k);
+        ws_bytes = ws > ws_bytes ? ws : ws_bytes;
+    }
+    std::lock_guard<std::mutex> lock(staging().mu);
+    void* base = nullptr;
+    cudaStream_t unused = nullptr;
+    cudaError_t err = staging_get(total + align_up(ws_bytes, 256), &base, &unused);
+    if (err != cudaSuccess) return err;
+    BatchContext* ctx = nullptr;
+    if ((err = batch_context(n_calls, &ctx)) != cudaSuccess) return err;
+    int* status = status_ptr();
+    if (!status) return cudaErrorInitializationError;
+    char* p = static_cast<char*>(base);
+    float* ws = ws_bytes ? reinterpret_cast<float*>(p + total) : nullptr;   // one workspace: the layers run in order on one stream
+    for (int i = 0; i < n_calls && err == cudaSuccess; i++) {
+        const fp6b200_host_call& c = calls[i];
+        const size_t act_bytes = c.N * c.K * sizeof(__half), out_bytes = c.N * c.M * sizeof(__half);
+        __half* act = reinterpret_cast<__half*>(p);
+        __half* out = reinterpret_cast<__half*>(p + align_up(act_bytes, 256));
+        p += align_up(act_bytes, 256) + align_up(out_bytes, 256);
+        cudaEvent_t landed = ctx->events[2 * i], done = ctx->events[2 * i + 1];
+        if ((err = cudaMemcpyAsync(act, c.act_host, act_bytes, cudaMemcpyHostToDevice, ctx->in)) != cudaSuccess) break;
+        if ((err = cudaEventRecord(landed, ctx->in)) != cudaSuccess) break;
+        if ((err = cudaStreamWaitEvent(ctx->compute, landed, 0)) != cudaSuccess) break;
+        err = fpx::launch_gemm(c.e_bits, c.m_bits, ctx->compute, c.weight_packed_dev, static_cast<const __half*>(c.scales_dev),
+                               act, out, c.M, c.N, c.K, ws, c.split_k, status);
+        if (err != cudaSuccess) break;
+        if ((err = cudaEventRecord(done, ctx->compute)) != cudaSuccess) break;
+        if ((err = cudaStreamWaitEvent(ctx->out, done, 0)) != cudaSuccess) break;
+        err = cudaMemcpyAsync(c.out_host, out, out_bytes, cudaMemcpyDeviceToHost, ctx->out);
+    }
+    // whatever was queued must finish before the staging buffer may be reused, error or not
+    const cudaError_t e1 = cudaStreamSynchronize(ctx->in), e2 = cudaStreamSynchronize(ctx->compute), e3 = cudaStreamSynchronize(ctx->out);
+    if (err != cudaSuccess) return err;
+    return e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3);
 }
 
 int fp6b200_prepack(int e_bits, int m_bits, void* stream, const void* unpacked_dev, void* packed_dev, size_t M,

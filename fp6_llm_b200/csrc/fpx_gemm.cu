@@ -61,22 +61,19 @@ constexpr int kActProducerWarp = kFirstDequantWarp + kDequantWarps;   // the las
 constexpr int kWarps = kActProducerWarp + 1;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kTmemCols = 512;      // the whole tensor memory: one CTA per SM
-// Sleep between two polls of a barrier (ns).  The copy producers run stages ahead of their consumers and an issuing warp
-// gets a new position only every few hundred nanoseconds; each failed poll costs issue slots the unpack warps need.
-#ifndef FPX_POLL_PRODUCER
-#define FPX_POLL_PRODUCER 200
-#endif
-#ifndef FPX_POLL_ISSUER
-#define FPX_POLL_ISSUER 40
-#endif
-constexpr uint32_t kPollProducer = FPX_POLL_PRODUCER;
-constexpr uint32_t kPollIssuer = FPX_POLL_ISSUER;
+
 
 // status codes written by a wait that gave up
 enum : int {
     kErrStageEmpty = 1, kErrStageFull = 2, kErrAEmpty = 3, kErrAFull = 6, kErrAccFull = 7, kErrSmemAlign = 8,
     kErrAccEmpty = 9, kErrPeerWait = 10   // 10: a peer GPU did not arrive at the end of a sharded layer
 };
+
+// Sleep between two polls of a barrier (ns).  Each failed poll costs issue slots the unpack warps need, so with the
+// long stages of the narrow tiles the copy producers (which run stages ahead of their consumers) and the issuing warps
+// (which get a new position only every few hundred nanoseconds) poll slowly; the wide tiles have stages of ~250 ns and
+// poll quickly.
+constexpr uint32_t kPollProducerNarrow = 200, kPollIssuerNarrow = 40, kPollWide = 20, kPollUnpackWide = 100;
 
 // Packed bytes of one (64 rows x 64 K) block per segment width.
 template <int BW>
@@ -104,8 +101,12 @@ struct Config {
     static constexpr int ks = gemm_ks(N_TILE);
     static constexpr int kpw = N_TILE <= 128 ? 2 : 1;
     static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : 4) : 4;
-    static constexpr int a_slots = 256 / (kpw * (int)kAColsPerKBlock);   // 256 columns of fp16 weights: 4 or 8 slots
+    static constexpr int a_slots = 4;   // one slot per unpack group: 4 x 64 columns of fp16 weights, 4 x 32 for the widest tile
     static constexpr int pos_per_stage = ks / kpw;
+    // When every stage is one position and the two rings are equally deep, slot and stage coincide and ONE commit of the
+    // issuing warp frees both the tensor-memory slot and the stage's activations (measured 6 % faster on the widest
+    // tile than two commits; the weights of a stage are still handed back by the unpack warps as soon as they are read).
+    static constexpr bool unified = (ks == kpw) && (a_slots == stages);
     // One thread can issue an MMA only every ~45-130 cycles and the narrow MMAs occupy the tensor pipe for ~40 only,
     // so narrow tiles are issued by several warps, each into an accumulator of its own (the epilogue adds them up).
     static constexpr int issuers = N_TILE <= 64 ? 4 : (N_TILE <= 128 ? 2 : 1);
@@ -124,6 +125,10 @@ struct Config {
                   "a slot is always consumed by the same issuing warp");
     static_assert(issuers <= kMaxIssuers, "issuing warps are the first warps of the CTA");
     static constexpr int readers = 4 * pos_per_stage;   // unpack warps that read a stage's weights
+    static constexpr uint32_t poll_producer = N_TILE <= 64 ? kPollProducerNarrow : kPollWide;
+    static constexpr uint32_t poll_issuer = N_TILE <= 64 ? kPollIssuerNarrow : kPollWide;
+    // the unpack warps of a wide tile are ahead of the tensor pipe most of the time: every poll they save is power for it
+    static constexpr uint32_t poll_unpack = N_TILE <= 128 ? ptx::kPollFast : kPollUnpackWide;
     static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
     static constexpr uint32_t w_off = ks * b_block;
     static constexpr uint32_t off1 = w_off;
@@ -265,7 +270,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             const uint8_t* reg2 = p.region[1];
             const uint8_t* reg4 = p.region[2];
             const uint32_t my_full = acts ? b_full : w_full;
-            const uint32_t my_empty = acts ? b_empty : w_empty;
+            const uint32_t my_empty = acts ? (Cfg::unified ? a_empty : b_empty) : w_empty;
             bool waited = !acts && p.weights_static != 0;   // nothing to wait for before static weights are read
             ptx::RingPos<R> pos;
             pos.set(0);
@@ -286,7 +291,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     const uint32_t kb_off = sidx * KS;
                     const uint32_t cnt = seg.nkb - kb_off < (uint32_t)KS ? seg.nkb - kb_off : (uint32_t)KS;
                     sidx = sidx + 1 == nstages ? 0u : sidx + 1;
-                    if (!PROF_WAIT(0, ptx::mbar_wait(my_empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, kPollProducer))) { ok = false; break; }
+                    if (!PROF_WAIT(0, ptx::mbar_wait(my_empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, Cfg::poll_producer))) { ok = false; break; }
                     PROF_COUNT(6)
                     if (!waited) {
                         asm volatile("griddepcontrol.wait;" ::: "memory");   // first read of memory the previous kernel may write
@@ -317,7 +322,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
                 const uint32_t first = issued > (uint32_t)R ? issued - R : 0u;
                 for (uint32_t t = first; t < issued; t++)
-                    ptx::mbar_wait(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, kPollProducer, 50000000ull);
+                    ptx::mbar_wait(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, Cfg::poll_producer, 50000000ull);
             }
         }
         __syncwarp();
@@ -364,7 +369,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::stage_bytes >> 4));
 #pragma unroll
                     for (uint32_t sub = sub0; sub < PPS; sub += (uint32_t)NI) {
-                        if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull, kPollIssuer))) { ok = false; break; }
+                        if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull, Cfg::poll_issuer))) { ok = false; break; }
                         if (me == 0 && nseg == 0 && t == 0) PROF_STAMP(5);
                         PROF_BEGIN(t_issue)
                         ptx::tc_fence_after_sync();
@@ -388,7 +393,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                         ap.advance(NI);
                     }
                     if (!ok) break;
-                    ptx::tc_commit(b_empty + 8 * rp.idx);
+                    if (!Cfg::unified) ptx::tc_commit(b_empty + 8 * rp.idx);
                     if (me == 0) PROF_STAMP(6);
                     rp.advance(IST);
                 }
@@ -538,7 +543,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 slot = ap.idx; slot_lap = ap.lap; slot_primed = 1;
             }
             for (; t < nstages; t += ST) {
-                if (!PROF_WAIT(0, ptx::mbar_wait_warp(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                if (!PROF_WAIT(0, ptx::mbar_wait_warp(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull, Cfg::poll_unpack))) { ok = false; break; }
                 if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == cls) PROF_STAMP(4);
                 PROF_COUNT(6)
                 const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
@@ -565,7 +570,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                         ptx::mbar_arrive_elected(w_empty + 8 * rp.idx);   // the weights can be refilled
                     }
                     if (b == 0) {
-                        if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * slot, slot_lap ^ 1u, abort_word, kErrAEmpty))) { ok = false; break; }
+                        if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * slot, slot_lap ^ 1u, abort_word, kErrAEmpty, Cfg::poll_unpack))) { ok = false; break; }
                         ptx::tc_fence_after_sync();
                     }
                     ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock, v[0]);
@@ -626,10 +631,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
 // (Summing inside the GEMM by the CTA that delivers a tile's last part was measured slower: its dependent global
 // round trips cost more than this launch, and wide tiles are then summed by one SM instead of all.)
 constexpr int kFixupCols = 16;
-#ifndef FPX_EVEN_PCT
-#define FPX_EVEN_PCT 85
-#endif
-constexpr uint64_t kEvenGridMinPercent = FPX_EVEN_PCT;
+constexpr uint64_t kEvenGridMinPercent = 85;
+constexpr uint64_t kFixupCostUnits = 20;   // the fix-up launch and its dependency cost about as much as 20 K blocks on one CTA
 constexpr uint64_t kMinUnitsPerCta = 8;   // a CTA is not started for fewer 64-K blocks than this (two 256-K stages)
 __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
                                                                          uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan,
@@ -756,18 +759,59 @@ cudaError_t make_act_map(CUtensorMap* map, const __half* act, size_t N, size_t K
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// The work decomposition of one call (see WorkPlan): split_k == 0 is the library's own (data-parallel waves of tiles,
+// then the K blocks of the remaining tiles dealt out evenly), split_k >= 1 the caller's.  Returns the effective split.
+int make_plan(size_t M, size_t n_tiles, size_t K, int split_k, int sms, WorkPlan* out) {
+    WorkPlan& plan = *out;
+    plan.m_tiles = (uint32_t)(M / kTileM);
+    plan.n_tiles = (uint32_t)n_tiles;
+    plan.kblocks = (uint32_t)(K / kKBlock);
+    const uint64_t tiles = (uint64_t)plan.m_tiles * plan.n_tiles;
+    int eff_split = 1;
+    if (split_k == 0) {
+        plan.mode = kStreamK;
+        plan.split_k = 1;
+        const uint64_t units = tiles * plan.kblocks;
+        // Fewer tiles than SMs: one CTA per whole tile (no tile is split, so no fix-up kernel follows) when that costs no
+        // more than dealing the K blocks out evenly plus the fix-up, which is worth about kFixupCostUnits K blocks.
+        if (tiles <= (uint64_t)sms && plan.kblocks <= units / (uint64_t)sms + kFixupCostUnits) {
+            plan.grid = (uint32_t)tiles;
+            plan_finalize(&plan);
+            return eff_split;
+        }
+        uint64_t cap = units / kMinUnitsPerCta;     // CTAs that still get kMinUnitsPerCta blocks each, at least one per tile
+        if (cap < tiles) cap = tiles;
+        if (cap > (uint64_t)sms) cap = (uint64_t)sms;
+        plan.grid = (uint32_t)cap;
+        // Fewer tiles than SMs: a grid that is a multiple of the tile count gives every tile the same number of
+        // CTAs and no CTA a second tile (one epilogue per CTA); taken when it still fills most of the SMs.
+        if (tiles < cap) {
+            const uint64_t even = tiles * (cap / tiles);
+            if (even * 100 >= cap * kEvenGridMinPercent) plan.grid = (uint32_t)even;
+        }
+    } else {              // the caller's split: splits beyond the number of K blocks would be empty
+        plan.mode = kClassic;
+        eff_split = split_k < (int)plan.kblocks ? split_k : (int)plan.kblocks;
+        plan.split_k = (uint32_t)eff_split;
+        const uint64_t items = tiles * eff_split;
+        plan.grid = (uint32_t)(items < (uint64_t)sms ? items : (uint64_t)sms);
+    }
+    plan_finalize(&plan);
+    return eff_split;
+}
+
 template <int BW, int N_TILE>
 cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
     auto kernel = fpx_gemm_kernel<BW, N_TILE>;
     constexpr uint32_t smem = Config<BW, N_TILE>::smem_bytes;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];   // zero-initialised; several host threads may launch at once
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return err;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     // Programmatic launch: the CTAs may start, set up and find their work while the previous kernel of the stream is
     // still finishing; every role waits (griddepcontrol.wait) before it first touches global memory.
@@ -807,15 +851,25 @@ extern "C" int fp6b200_debug_read_stamps(unsigned long long* host_out) {
 #endif
 
 int device_sm_count() {
-    static int counts[64] = {};
+    static std::atomic<int> counts[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (!counts[dev]) {
-        int n = 0;
+    int n = counts[dev].load(std::memory_order_relaxed);
+    if (!n) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        counts[dev] = n;
+        counts[dev].store(n, std::memory_order_relaxed);
     }
-    return counts[dev];
+    return n;
+}
+
+int gemm_kernel_launches(size_t M, size_t N, size_t K, int split_k) {
+    if (M == 0 || M % 256 != 0 || K == 0 || K % 64 != 0 || N == 0 || split_k < 0) return 0;
+    const int n_tile = gemm_n_tile(N);
+    const int sms = device_sm_count() < (int)kMaxGrid ? device_sm_count() : (int)kMaxGrid;
+    WorkPlan plan;
+    const int eff_split = make_plan(M, (N + n_tile - 1) / n_tile, K, split_k, sms, &plan);
+    if (plan.mode == kStreamK) return plan_rem_tiles(plan) ? 2 : 1;   // GEMM (+ fix-up of the split tiles)
+    return eff_split > 1 ? 2 : 1;                                     // GEMM (+ split-K reduction)
 }
 
 int gemm_n_tile(size_t N) { return N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256))); }
@@ -902,33 +956,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     prm.K = (uint32_t)K;
     prm.status = status;
     WorkPlan& plan = prm.plan;
-    plan.m_tiles = (uint32_t)(M / kTileM);
-    plan.n_tiles = (uint32_t)n_tiles;
-    plan.kblocks = (uint32_t)(K / kKBlock);
-    const uint64_t tiles = (uint64_t)plan.m_tiles * plan.n_tiles;
-    int eff_split = 1;
-    if (split_k == 0) {   // the library's own decomposition: data-parallel waves + stream-K remainder
-        plan.mode = kStreamK;
-        plan.split_k = 1;
-        const uint64_t units = tiles * plan.kblocks;
-        uint64_t cap = units / kMinUnitsPerCta;     // CTAs that still get kMinUnitsPerCta blocks each, at least one per tile
-        if (cap < tiles) cap = tiles;
-        if (cap > (uint64_t)sms) cap = (uint64_t)sms;
-        plan.grid = (uint32_t)cap;
-        // Fewer tiles than SMs: a grid that is a multiple of the tile count gives every tile the same number of
-        // CTAs and no CTA a second tile (one epilogue per CTA); taken when it still fills most of the SMs.
-        if (tiles < cap) {
-            const uint64_t even = tiles * (cap / tiles);
-            if (even * 100 >= cap * kEvenGridMinPercent) plan.grid = (uint32_t)even;
-        }
-    } else {              // the caller's split: splits beyond the number of K blocks would be empty
-        plan.mode = kClassic;
-        eff_split = split_k < (int)plan.kblocks ? split_k : (int)plan.kblocks;
-        plan.split_k = (uint32_t)eff_split;
-        const uint64_t items = tiles * eff_split;
-        plan.grid = (uint32_t)(items < (uint64_t)sms ? items : (uint64_t)sms);
-    }
-    plan_finalize(&plan);
+    const int eff_split = make_plan(M, n_tiles, K, split_k, sms, &plan);
     const int bw = 1 + e_bits + m_bits;
     err = bw == 6 ? launch_by_n<6>(n_tile, stream, map, prm) : launch_by_n<5>(n_tile, stream, map, prm);
     if (err != cudaSuccess) return err;

@@ -42,6 +42,8 @@ int weights_static();
 void set_programmatic_launch(int on);
 int programmatic_launch();
 int gemm_n_tile(size_t N);
+// Kernels one GEMM call launches on the current device (0 for an invalid shape).
+int gemm_kernel_launches(size_t M, size_t N, size_t K, int split_k);
 int device_sm_count();
 // Workspace the GEMM needs when it picks its own decomposition (split_k == 0).
 size_t gemm_auto_workspace_bytes(size_t N);

@@ -35,7 +35,7 @@ def HeuristicFuntion_SplitK(M, N, Num_GPU_SMs):
 
 
 def heuristic_split_k_b200(M: int, N: int, K: int, num_sms: int = 148) -> int:
-    """Split-K for the sm_100a kernel: 128-row tiles, 1 or 2 CTAs per SM, K-aware (C: fp6b200_choose_split_k)."""
+    """Split-K for the sm_100a kernel: 128-row tiles, one CTA per SM, K-aware (C: fp6b200_choose_split_k)."""
     return int(_native.lib().fp6b200_choose_split_k(M, N, K, num_sms))
 
 
@@ -54,15 +54,21 @@ def _ptr(t: torch.Tensor) -> ctypes.c_void_p:
 
 
 _workspaces: dict = {}
+_retired: list = []
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
-    """Grow-only fp32 split-K workspace per device (the reference allocates one per call,
-    fp6_llm/csrc/fp6_linear.cu:185-187).  Calls that share it must be ordered on one stream."""
-    ws = _workspaces.get(device)
+    """Grow-only fp32 split-K workspace per (device, stream) (the reference allocates one per call,
+    fp6_llm/csrc/fp6_linear.cu:185-187): calls on one stream run in order and may share it, calls on different
+    streams get their own.  A buffer that is outgrown is kept alive until the process ends, because work already
+    queued (or captured in a CUDA graph) may still use it."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
     if ws is None or ws.numel() * 4 < nbytes:
+        if ws is not None:
+            _retired.append(ws)
         ws = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=device)
-        _workspaces[device] = ws
+        _workspaces[key] = ws
     return ws
 
 
@@ -137,8 +143,9 @@ def weight_prepacking_eXmY_cpu(EXPONENT: int, MANTISSA: int, fpx_tensor: torch.T
     """Unpacked int32 [OC, IC/32*bw] -> prepacked tensor of the same shape, bit-identical to the reference's
     weight_matrix_prepacking_fp_eXmY_cpu (fp6_llm/csrc/fp6_linear.cu:323-341).
 
-    A CPU tensor (the reference's case) is staged through the GPU and a CPU tensor comes back; a CUDA tensor
-    is packed in place on its device.  Either way the packing itself runs in the CUDA kernel."""
+    A CPU tensor (the reference's case) is staged through the GPU and a CPU tensor comes back; a CUDA tensor is
+    packed on its device into a NEW tensor (the device kernel gathers from all over the matrix and cannot work in
+    place).  Either way the packing itself runs in the CUDA kernel."""
     _require_cuda()
     check_format(EXPONENT, MANTISSA)
     if fpx_tensor.dtype != torch.int32 or fpx_tensor.dim() != 2:
@@ -250,6 +257,33 @@ def linear_forward_host(EXPONENT: int, MANTISSA: int, act_host: torch.Tensor, pa
                                                   _ptr(out_host), OC, B, IC, splitK)
     _native.check(rc, "fp6b200_linear_host_io")
     return out_host
+
+
+def linear_forward_host_batch(calls) -> None:
+    """Several host-buffer layers as one pipelined batch (C: fp6b200_linear_host_io_batch): `calls` is a sequence of
+    (EXPONENT, MANTISSA, act_host, packed_dev, scales_dev, out_host, splitK); host tensors should be pinned.  The copy of
+    the next call's activations and of the previous call's result overlap the current call's kernels; returns when
+    every output has arrived."""
+    _require_cuda()
+    calls = list(calls)
+    if not calls:
+        return
+    arr = (_native.HostCall * len(calls))()
+    dev = calls[0][3].device
+    for i, (e, m, act, packed, scales, out, split_k) in enumerate(calls):
+        check_format(e, m)
+        if packed.device != dev or scales.device != dev:
+            raise ValueError("all layers of a batch must live on one device")
+        if act.is_cuda or out.is_cuda or act.dtype != torch.float16 or out.dtype != torch.float16:
+            raise ValueError("activations and outputs of the host entry points are fp16 CPU tensors")
+        B, IC = act.shape
+        OC = packed.shape[0]
+        if _in_channels(packed, e, m) != IC or tuple(out.shape) != (B, OC) or not (act.is_contiguous() and out.is_contiguous()):
+            raise ValueError("shape mismatch between activations, packed weights and output")
+        arr[i] = _native.HostCall(e, m, packed.data_ptr(), scales.data_ptr(), act.data_ptr(), out.data_ptr(), OC, B, IC, split_k)
+    with torch.cuda.device(dev):
+        rc = _native.lib().fp6b200_linear_host_io_batch(arr, len(calls))
+    _native.check(rc, "fp6b200_linear_host_io_batch")
 
 
 def set_static_weights(on: bool) -> None:

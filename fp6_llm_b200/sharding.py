@@ -90,17 +90,29 @@ def gather_columns(local: torch.Tensor, plan: Sequence[Tuple[int, int]], rank: i
 
 class PeerExchange:
     """What the ranks of one process group share for the fused exchange: a flag word per pair of ranks, this rank's
-    call counter, and two alternating output buffers per (batch, out_channels) shape, all but the counter in symmetric
+    call counter, and three rotating output buffers per (batch, out_channels) shape, all but the counter in symmetric
     memory (torch.distributed._symmetric_memory: every rank's allocation is mapped into every process).
 
-    A rank can run at most one layer ahead of a peer (each layer ends with the arrival barrier), so a result stays
-    valid until the second next layer of the same shape is started on this rank: consume it (on the same stream)
-    before that, or copy it."""
+    Lifetime of a result.  Every call ends with the arrival barrier, so a rank runs at most one call ahead of a peer,
+    and a peer stores into a buffer as soon as it starts the call that uses it.  With three buffers per shape the
+    tensor returned by call k is overwritten by call k+3 of that shape, which a peer may start once THIS rank has
+    issued call k+2: a result is safe while this rank issues one more call of the shape (h1 = L1(x); h2 = L2(h1);
+    y = h1 + h2 is fine), and must be consumed or copied, in stream order, before the second next one is issued.
+
+    CUDA graphs.  The buffer is chosen on the host when the call is made, so a captured graph always uses the buffers
+    it was captured with: capture a multiple of three calls per shape, or make sure that in every replay order two
+    calls that share a buffer are at least three layer calls (of any shape: each ends with the barrier) apart.
+
+    Multicast is switched off for the symmetric allocations (the kernels use plain peer stores only): call close()
+    - after a barrier between the ranks - before the process group is destroyed."""
 
     MAX_WORLD = 8
+    BUFFERS = 3
 
     def __init__(self, group=None):
+        import os
         import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # before the first rendezvous of the process
         import torch.distributed._symmetric_memory as symm
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -118,19 +130,28 @@ class PeerExchange:
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._flags_handle.buffer_ptrs])
         self._buffers = {}
 
+    def close(self) -> None:
+        """Drops the exchange buffers and their peer mappings.  Collective in spirit: every rank must have finished its
+        calls (synchronise, then a barrier between the ranks) before any rank closes."""
+        torch.cuda.synchronize(self.device)
+        self._buffers = {}
+        self._flag_ptrs = None
+        self._flags_handle = None
+        self.flags = None
+
     def _next_buffer(self, batch: int, out_channels: int):
         key = (batch, out_channels)
         slot = self._buffers.get(key)
         if slot is None:
-            pair = []
-            for _ in range(2):
+            ring = []
+            for _ in range(self.BUFFERS):
                 t = self._symm.empty((batch, out_channels), dtype=torch.float16, device=self.device)
                 h = self._symm.rendezvous(t, self.group)
-                pair.append((t, h, (ctypes.c_void_p * self.world)(*[int(p) for p in h.buffer_ptrs])))
-            slot = {"pair": pair, "next": 0}
+                ring.append((t, h, (ctypes.c_void_p * self.world)(*[int(p) for p in h.buffer_ptrs])))
+            slot = {"ring": ring, "next": 0}
             self._buffers[key] = slot
-        entry = slot["pair"][slot["next"]]
-        slot["next"] ^= 1
+        entry = slot["ring"][slot["next"]]
+        slot["next"] = (slot["next"] + 1) % self.BUFFERS
         return entry
 
     def reserve(self, batch: int, out_channels: int) -> None:

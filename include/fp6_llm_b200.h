@@ -50,8 +50,30 @@ int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_pack
 int fp6b200_linear_host_io(int e_bits, int m_bits, const void* weight_packed_dev, const void* scales_dev,
                            const void* act_host, void* out_host, size_t M, size_t N, size_t K, int split_k);
 
+/*
+ * Several such layers as ONE pipelined batch: the activations of call i+1 are copied to the device and the result of
+ * call i-1 is copied back while call i computes (three internal streams chained by events, one copy per buffer, one
+ * synchronisation at the end; the calls compute in array order).  Host buffers should be pinned, or the copies do not
+ * overlap.  Stands in for a sequence of fp_eXmY_linear_forward_cuda calls (fp6_llm/csrc/fp6_linear.cu:269-313) made
+ * on host tensors; the reference has no batched form.  Returns the first error; no call's output is valid then.
+ */
+typedef struct fp6b200_host_call {
+    int e_bits, m_bits;
+    const void* weight_packed_dev;
+    const void* scales_dev;
+    const void* act_host;   /* fp16 [N][K] */
+    void* out_host;         /* fp16 [N][M] */
+    size_t M, N, K;
+    int split_k;            /* as for fp6b200_linear; 0 = library decomposition */
+} fp6b200_host_call;
+int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls);
+
 /* Bytes of split-K workspace fp6b200_linear needs (split_k == 0: for the library's own choice). */
 size_t fp6b200_workspace_bytes(size_t M, size_t N, size_t K, int split_k);
+
+/* Number of kernels fp6b200_linear launches for this shape on the current device: the GEMM, plus the split-K reduction
+ * or the fix-up of split tiles when the decomposition needs one (no counterpart in the reference; used to count launches). */
+int fp6b200_kernel_launches(size_t M, size_t N, size_t K, int split_k);
 
 /*
  * Split count for callers that keep the reference's explicit split-K scheme: the best split_k >= 1 for this

@@ -33,7 +33,7 @@ def test_cxx_names_of_the_reference_are_exported(native_lib):
 
 
 def test_version_and_error_text(native_lib):
-    assert native_lib.fp6b200_version() == 1
+    assert native_lib.fp6b200_version() == 2
     assert b"invalid" in native_lib.fp6b200_error_string(1).lower()
 
 

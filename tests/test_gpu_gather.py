@@ -112,7 +112,7 @@ def test_gather_rejects_bad_arguments(native_lib):
 def test_one_process_per_gpu():
     """One process per GPU (2, 4 or 8 of them): symmetric-memory buffers, peer stores over NVLink, the barrier
     between real ranks."""
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     ranks = max(n for n in (2, 4, 8) if n <= torch.cuda.device_count())
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(ROOT, "tests", "gather_worker.py")]
