@@ -25,9 +25,19 @@ _ORACLE_SO = os.path.join(_HERE, "_build", "liboracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libfp6_ref.so")
 
 
+def _find_reference() -> str | None:
+    """A checkout of the reference project: $FP6_LLM_REFERENCE, else a `reference` folder beside this repository."""
+    cand = [os.environ.get("FP6_LLM_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cand:
+        if c and os.path.isdir(os.path.join(c, "fp6_llm", "csrc")):
+            return c
+    return None
+
+
 def build(reference_root: str | None = None) -> None:
-    """Compile the C restatement and, when the reference tree exists, oracle/_ref."""
+    """Compile the C restatement and, when a checkout of the reference is found, oracle/_ref from its sources."""
     args = ["make", "-s", "-C", _HERE, "all"]
+    reference_root = reference_root or _find_reference()
     if reference_root:
         args.append(f"REFERENCE_ROOT={reference_root}")
     subprocess.run(args, check=True)

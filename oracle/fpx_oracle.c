@@ -163,7 +163,11 @@ int oracle_prepack(int e_bits, int m_bits, uint8_t* out, const uint8_t* in, size
         if (!(bw & seg_ws[s])) continue;
         lane_bytes[s] = rows * cols * seg_ws[s] / 8 / 32;
         lanes[s] = (uint8_t*)malloc(lane_bytes[s] * 32);
-        if (!lanes[s]) return -1;
+        if (!lanes[s]) {
+            for (int t = 0; t < s; t++) free(lanes[t]);
+            free(src);
+            return -1;
+        }
     }
     const size_t row_bytes = cols * bw / 8;
     /* Pass-1 (:141-157): walk 64-row blocks, 16-col blocks, 16-row sub-blocks;

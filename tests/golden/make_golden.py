@@ -1,6 +1,6 @@
 """Regenerates the fixtures in this folder from the REFERENCE implementation.
 
-Run in a checkout that has the reference tree (default /root/reference):
+Run where a checkout of the reference (usyd-fsalab/fp6_llm) is available; pass its path, or set FP6_LLM_REFERENCE:
     python tests/golden/make_golden.py [reference_root]
 
 * prepack_dequant_e{E}m{M}.npz : seeded random unpacked weights and scales, with the outputs of the reference's
@@ -23,7 +23,7 @@ import oracle  # noqa: E402
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else None   # a checkout of usyd-fsalab/fp6_llm; default: see oracle.build
     oracle.build(ref_root)
     assert oracle.have_ref(), "oracle/_ref was not built: reference tree missing?"
     rng = np.random.default_rng(20240607)

@@ -62,7 +62,7 @@ def test_config_4096_bs8(oracle_mod):
     _check(oracle_mod, y2, truth)
 
 
-@pytest.mark.parametrize("oc,ic", [(1024, 4096), (4096, 1024), (768, 11008)])
+@pytest.mark.parametrize("oc,ic", [(1024, 4096), (768, 11008)])
 @pytest.mark.parametrize("bs", [1, 32, 128])
 def test_llama7b_like_fp6(oracle_mod, oc, ic, bs):
     """Row slices of the LLaMA-2-7B layer shapes (full K), quantised N(0, 0.02) weights, heuristic split-K."""

@@ -8,22 +8,23 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _problem(oc, ic, bs, seed):
+def _problem(oc, ic, bs, seed, oracle_mod=None):
     import fp6_llm_b200 as f
     from fp6_llm_b200.formats import random_codes_layer
     w, s = random_codes_layer(oc, ic, 3, 2, seed, scale_lo=0.01, scale_hi=0.1)
     packed = f.weight_prepacking_cpu(w.cuda())
-    x = torch.randn(bs, ic, generator=torch.Generator().manual_seed(seed + 1)).half().cuda()
-    return packed, s.cuda(), x
+    x = torch.randn(bs, ic, generator=torch.Generator().manual_seed(seed + 1)).half()
+    truth = oracle_mod.linear(x.numpy(), w.numpy(), s.numpy(), 3, 2) if oracle_mod is not None else None
+    return packed, s.cuda(), x.cuda(), truth
 
 
-def test_static_scratch_matches_workspace_entry(native_lib):
+def test_static_scratch_matches_workspace_entry(native_lib, oracle_mod):
     import fp6_llm_b200 as f
     L = native_lib
     # two different problems back to back: 32 tiles dealt over all SMs (every tile goes through the scratch), then a
     # shape whose remainder tiles do
     for oc, ic, bs, seed in ((4096, 2048, 8, 3), (1536, 4096, 40, 4)):
-        packed, s, x = _problem(oc, ic, bs, seed)
+        packed, s, x, truth = _problem(oc, ic, bs, seed, oracle_mod)
         expect = f.linear_forward_cuda(x, packed, s, 0)                   # ordinary entry point, caller-owned workspace
         for _ in range(2):
             out = torch.full((bs, oc), float("nan"), dtype=torch.float16, device="cuda")
@@ -35,11 +36,14 @@ def test_static_scratch_matches_workspace_entry(native_lib):
             err = (out.float() - expect.float()).norm() / expect.float().norm()
             assert err.item() <= 2e-3
             assert torch.equal(out, expect)
+            # and against the oracle itself (reference dequantisation + fp32 matmul), with the linear layer's tolerances
+            res = oracle_mod.check_tolerance(out.float().cpu().numpy(), truth)
+            assert res["rel_fro"] <= 2e-3 and res["max_row_rel"] <= 1e-2, res
 
 
 def test_static_scratch_refuses_oversized_problems(native_lib):
     L = native_lib
-    packed, s, x = _problem(256, 256, 4, 5)
+    packed, s, x, _ = _problem(256, 256, 4, 5)
     assert L.fp6b200_static_scratch_bytes() == 10 << 20
     big_n = 4096                                                          # 256-wide tiles: far more scratch than the array
     assert L.fp6b200_workspace_bytes(256, big_n, 256, 0) > L.fp6b200_static_scratch_bytes()
