@@ -183,10 +183,11 @@ struct Params {
     int* status;
 };
 
-template <int BW, int N_TILE>
+template <int E_BITS, int M_BITS, int N_TILE>
 __global__ void __launch_bounds__(kThreads, 1)
 fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ Params p) {
-    constexpr int E_BITS = BW - 3;   // both supported formats have a 2-bit mantissa
+    constexpr int BW = 1 + E_BITS + M_BITS;
+    constexpr bool kShortUnpack = M_BITS == 2 && (E_BITS == 3 || E_BITS == 2);   // e3m2, e2m2: the multiply-based sequence
     using Cfg = Config<BW, N_TILE>;
     using Raw = typename Cfg::Raw;
     constexpr int KS = Cfg::ks;
@@ -556,7 +557,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
 #pragma unroll
                     for (int jj = 0; jj < 4; jj++) {
                         uint32_t pat[8];
-                        unpack16_mul<E_BITS>(w4[jj][0], w4[jj][1], w2[jj], w1[jj], km, pat);
+                        if constexpr (kShortUnpack) unpack16_mul<E_BITS>(w4[jj][0], w4[jj][1], w2[jj], w1[jj], km, pat);
+                        else unpack16_generic<E_BITS, M_BITS>(w4[jj][0], w4[jj][1], w2[jj], w1[jj], h, pat);
 #pragma unroll
                         for (int kk = 0; kk < 2; kk++)
 #pragma unroll
@@ -800,10 +802,10 @@ int make_plan(size_t M, size_t n_tiles, size_t K, int split_k, int sms, WorkPlan
     return eff_split;
 }
 
-template <int BW, int N_TILE>
+template <int E_BITS, int M_BITS, int N_TILE>
 cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
-    auto kernel = fpx_gemm_kernel<BW, N_TILE>;
-    constexpr uint32_t smem = Config<BW, N_TILE>::smem_bytes;
+    auto kernel = fpx_gemm_kernel<E_BITS, M_BITS, N_TILE>;
+    constexpr uint32_t smem = Config<1 + E_BITS + M_BITS, N_TILE>::smem_bytes;
     static std::atomic<bool> configured[64];   // zero-initialised; several host threads may launch at once
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
@@ -828,14 +830,14 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params
     return cudaLaunchKernelEx(&cfg, kernel, map, prm);
 }
 
-template <int BW>
+template <int E_BITS, int M_BITS>
 cudaError_t launch_by_n(int n_tile, cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
     switch (n_tile) {
-        case 16:  return launch_one<BW, 16>(stream, map, prm);
-        case 32:  return launch_one<BW, 32>(stream, map, prm);
-        case 64:  return launch_one<BW, 64>(stream, map, prm);
-        case 128: return launch_one<BW, 128>(stream, map, prm);
-        default:  return launch_one<BW, 256>(stream, map, prm);
+        case 16:  return launch_one<E_BITS, M_BITS, 16>(stream, map, prm);
+        case 32:  return launch_one<E_BITS, M_BITS, 32>(stream, map, prm);
+        case 64:  return launch_one<E_BITS, M_BITS, 64>(stream, map, prm);
+        case 128: return launch_one<E_BITS, M_BITS, 128>(stream, map, prm);
+        default:  return launch_one<E_BITS, M_BITS, 256>(stream, map, prm);
     }
 }
 
@@ -957,8 +959,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     prm.status = status;
     WorkPlan& plan = prm.plan;
     const int eff_split = make_plan(M, n_tiles, K, split_k, sms, &plan);
-    const int bw = 1 + e_bits + m_bits;
-    err = bw == 6 ? launch_by_n<6>(n_tile, stream, map, prm) : launch_by_n<5>(n_tile, stream, map, prm);
+    FPX_DISPATCH_FORMAT(e_bits, m_bits, (err = launch_by_n<kE, kM>(n_tile, stream, map, prm)));
     if (err != cudaSuccess) return err;
     if (plan.mode == kStreamK) {
         const uint32_t rem = plan_rem_tiles(plan);

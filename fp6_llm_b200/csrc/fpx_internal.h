@@ -7,8 +7,21 @@
 
 namespace fpx {
 
-// Only e3m2 (FP6) and e2m2 (FP5) exist in the reference (fp6_llm/csrc/fp6_linear.cu:133-138).
-inline bool format_supported(int e_bits, int m_bits) { return m_bits == 2 && (e_bits == 3 || e_bits == 2); }
+// The reference's launcher knows e3m2 (FP6) and e2m2 (FP5) only (fp6_llm/csrc/fp6_linear.cu:133-138), but its packer and
+// dequantiser are templates over any code narrower than 8 bits (fp6_llm/csrc/utils/weight_prepacking.h:118-128,
+// fp6_llm/csrc/utils/weight_dequant.h:10-48).  Here: those two plus e2m1 (4-bit), e3m1 (5-bit) and e2m3 (6-bit).
+inline bool format_supported(int e_bits, int m_bits) {
+    return (m_bits == 2 && (e_bits == 3 || e_bits == 2)) || (m_bits == 1 && (e_bits == 2 || e_bits == 3)) || (m_bits == 3 && e_bits == 2);
+}
+// Runs CALL with the format as the compile-time constants kE and kM.
+#define FPX_DISPATCH_FORMAT(e_bits, m_bits, CALL)                                   \
+    do {                                                                            \
+        if ((e_bits) == 3 && (m_bits) == 2) { constexpr int kE = 3, kM = 2; CALL; }   \
+        else if ((e_bits) == 2 && (m_bits) == 2) { constexpr int kE = 2, kM = 2; CALL; } \
+        else if ((e_bits) == 2 && (m_bits) == 1) { constexpr int kE = 2, kM = 1; CALL; } \
+        else if ((e_bits) == 3 && (m_bits) == 1) { constexpr int kE = 3, kM = 1; CALL; } \
+        else { constexpr int kE = 2, kM = 3; CALL; }                                  \
+    } while (0)
 
 // Where the fp16 result goes.  One target with ld == M and row0 == 0 is the plain layer.  Several targets are the
 // output buffers [N][ld] of the ranks of an OC-sharded layer (this GPU's and its peers', as mapped into this

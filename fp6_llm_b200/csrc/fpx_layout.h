@@ -148,6 +148,40 @@ FPX_HD void unpack16(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, int h
     out[4] = expand_13(y2); out[5] = expand_02(y2); out[6] = expand_13(y3); out[7] = expand_02(y3);
 }
 
+// The general case: any format whose code is at most 6 bits wide (e2m1, e3m1, e2m3 besides the two above).  Every
+// byte first receives its code left-aligned, [code | 0...], the way the reference's dequantiser assembles it
+// (utils_parallel_dequant.cuh:63-86: the 1-, 2- and 4-bit segments are masked at the top of each byte and shifted
+// right by the width of the segments above them); the bytes are then spread into 16-bit lanes and everything but
+// the sign is shifted right by 5 - E (FPx_FP16_Cast_4Way, :13-28).  About twice the instructions of the two
+// sequences above, which exist because e3m2 and e2m2 are the formats that matter.
+template <int E_BITS, int M_BITS>
+FPX_HD void unpack16_generic(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, int h, uint32_t out[8]) {
+    constexpr int BW = 1 + E_BITS + M_BITS;
+    static_assert(BW >= 4 && BW <= 6 && E_BITS >= 1 && E_BITS <= 5, "one or two segments: 4-bit, 1+4-bit or 2+4-bit codes");
+    constexpr int kAbove4 = BW - 4;   // bits of the code above its 4-bit segment (0, 1 or 2)
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+    for (int n = 0; n < 4; n++) {
+        const uint32_t w4 = n < 2 ? w4a : w4b;
+        const uint32_t nib = ((n & 1) ? (w4 << 4) : w4) & 0xf0f0f0f0u;     // the 4-bit segment at the top of every byte
+        uint32_t code = nib >> kAbove4;
+        if (BW == 5) code |= (w1 << (4 * h + n)) & 0x80808080u;           // iteration 4h+n of the 1-bit word
+        if (BW == 6) code |= (w2 << (2 * n)) & 0xc0c0c0c0u;               // iteration n of the 2-bit word
+        // bytes 3,1 and bytes 2,0 as the high bytes of two 16-bit lanes each; sign stays, the rest moves down
+        const uint32_t a = expand_13(code), b = expand_02(code);
+        out[2 * n] = (a & 0x80008000u) | ((a & 0x7fff7fffu) >> (5 - E_BITS));
+        out[2 * n + 1] = (b & 0x80008000u) | ((b & 0x7fff7fffu) >> (5 - E_BITS));
+    }
+}
+
+// What the kernels call: the short sequences for e3m2 / e2m2, the general one otherwise.
+template <int E_BITS, int M_BITS>
+FPX_HD void unpack16_any(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, int h, uint32_t out[8]) {
+    if (M_BITS == 2 && (E_BITS == 3 || E_BITS == 2)) unpack16<(M_BITS == 2 && E_BITS == 2) ? 2 : 3>(w4a, w4b, w2, w1, h, out);
+    else unpack16_generic<E_BITS, M_BITS>(w4a, w4b, w2, w1, h, out);
+}
+
 // The same unpack for the GEMM's inner loop, in fewer instructions and with part of them moved off the logic pipe.
 // On B200 the logic operations (LOP3, PRMT, funnel shifts) issue at 64 lanes per clock and SM, and integer
 // multiply-adds issue at the same rate on the other (FMA) pipe; the sequence above keeps only the logic pipe busy.
@@ -204,23 +238,23 @@ FPX_HD void unpack16_mul(uint32_t w4a, uint32_t w4b, uint32_t w2, uint32_t w1, c
     out[4] = expand_13(y[2]); out[5] = expand_02(y[2]); out[6] = expand_13(y[3]); out[7] = expand_02(y[3]);
 }
 
-// Round-to-nearest quantiser (2 mantissa bits).  Value of the non-negative code c: subnormals m/4 * 2^(1-bias),
-// otherwise (1 + m/4) * 2^(e-bias), bias = 2^(E-1) - 1 (28 is the largest e3m2 magnitude, 7 the largest e2m2 one).
-FPX_HD float fpx_magnitude(int e_bits, int c) {
+// Round-to-nearest quantiser.  Value of the non-negative code c = (e << M) | m: subnormals m / 2^M * 2^(1-bias),
+// otherwise (1 + m / 2^M) * 2^(e-bias), bias = 2^(E-1) - 1 (28 is the largest e3m2 magnitude, 7 the largest e2m2 one).
+FPX_HD float fpx_magnitude(int e_bits, int m_bits, int c) {
     const int bias = (1 << (e_bits - 1)) - 1;
-    const int e = c >> 2, m = c & 3;
-    const int p = (e == 0 ? 1 : e) - bias - 2;               // the value is (e == 0 ? m : 4 + m) * 2^p
+    const int e = c >> m_bits, m = c & ((1 << m_bits) - 1);
+    const int p = (e == 0 ? 1 : e) - bias - m_bits;          // the value is (e == 0 ? m : 2^M + m) * 2^p
     const float unit = p >= 0 ? (float)(1 << p) : 1.0f / (float)(1 << -p);
-    return (float)(e == 0 ? m : 4 + m) * unit;
+    return (float)(e == 0 ? m : (1 << m_bits) + m) * unit;
 }
 // Code (sign bit included) of the quotient q = w / scale: the nearest magnitude, ties to the even code, saturating;
 // the sign bit is the sign bit of q (so -0 keeps its sign).
-FPX_HD uint32_t quantize_rtn_code(int e_bits, float q) {
-    const int codes = 1 << (e_bits + 2);
+FPX_HD uint32_t quantize_rtn_code(int e_bits, int m_bits, float q) {
+    const int codes = 1 << (e_bits + m_bits);
     const float a = q < 0.0f ? -q : q;
     int below = 0, not_above = 0;                            // midpoints < a, midpoints <= a
     for (int c = 0; c + 1 < codes; c++) {
-        const float mid = 0.5f * (fpx_magnitude(e_bits, c) + fpx_magnitude(e_bits, c + 1));
+        const float mid = 0.5f * (fpx_magnitude(e_bits, m_bits, c) + fpx_magnitude(e_bits, m_bits, c + 1));
         below += mid < a ? 1 : 0;
         not_above += mid <= a ? 1 : 0;
     }

@@ -77,11 +77,11 @@ prepack_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32
 // weight_quant.h:9-104 truncates and is not bound; the layout it would feed is the packer's above.)
 // Code of a weight = nearest representable magnitude of |w / scale| (the division in fp32, round to nearest);
 // ties go to the even code; beyond the largest magnitude it saturates; the sign bit is the sign of the quotient.
-template <int BW>
+template <int E_BITS, int M_BITS>
 __global__ void __launch_bounds__(kPrepackThreads)
 quantize_prepack_kernel(const __half* __restrict__ w, const __half* __restrict__ scales, uint8_t* __restrict__ out,
                         uint32_t M, uint32_t K) {
-    constexpr int E_BITS = BW - 3;
+    constexpr int BW = 1 + E_BITS + M_BITS;
     constexpr uint32_t kCols = kChunkKBlocks * kKBlock;
     constexpr uint32_t kPitch = kCols + 4;
     __shared__ __align__(16) uint8_t codes[kRowsPerBlock * kPitch];
@@ -99,8 +99,8 @@ quantize_prepack_kernel(const __half* __restrict__ w, const __half* __restrict__
         const uint32_t row = i * kRowsPerBlock + r;
         const __half2 pair = *reinterpret_cast<const __half2*>(w + (size_t)row * K + col0 + c);
         const float sc = __half2float(scales[row]);
-        codes[r * kPitch + c] = (uint8_t)quantize_rtn_code(E_BITS, __fdiv_rn(__low2float(pair), sc));
-        codes[r * kPitch + c + 1] = (uint8_t)quantize_rtn_code(E_BITS, __fdiv_rn(__high2float(pair), sc));
+        codes[r * kPitch + c] = (uint8_t)quantize_rtn_code(E_BITS, M_BITS, __fdiv_rn(__low2float(pair), sc));
+        codes[r * kPitch + c + 1] = (uint8_t)quantize_rtn_code(E_BITS, M_BITS, __fdiv_rn(__high2float(pair), sc));
     }
     __syncthreads();
 
@@ -128,11 +128,11 @@ quantize_prepack_kernel(const __half* __restrict__ w, const __half* __restrict__
 }
 
 // Thread = 8 consecutive codes of one row (BW bytes in, 16 bytes out).
-template <int BW>
+template <int E_BITS, int M_BITS>
 __global__ void __launch_bounds__(256)
 dequant_unpacked_kernel(const uint8_t* __restrict__ in, const __half* __restrict__ scales, __half* __restrict__ out,
                         uint32_t M, uint32_t K) {
-    constexpr int E_BITS = BW - 3;
+    constexpr int BW = 1 + E_BITS + M_BITS;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // group of 8 codes
     const size_t groups_per_row = K / 8;
     if (idx >= (size_t)M * groups_per_row) return;
@@ -156,11 +156,11 @@ dequant_unpacked_kernel(const uint8_t* __restrict__ in, const __half* __restrict
 }
 
 // Warp = 32 rows x 64 columns, the unit one unpack warp of the GEMM handles per pipeline stage.
-template <int BW>
+template <int E_BITS, int M_BITS>
 __global__ void __launch_bounds__(128)
 dequant_packed_kernel(const uint8_t* __restrict__ packed, const __half* __restrict__ scales, __half* __restrict__ out,
                       uint32_t M, uint32_t K) {
-    constexpr int E_BITS = BW - 3;
+    constexpr int BW = 1 + E_BITS + M_BITS;
     const uint32_t kblocks = K / kKBlock;
     const uint32_t unit = blockIdx.x * 4 + (threadIdx.x >> 5);     // (64-row block, k-block, half)
     if (unit >= (M / kRowsPerBlock) * kblocks * 2) return;
@@ -179,7 +179,7 @@ dequant_packed_kernel(const uint8_t* __restrict__ packed, const __half* __restri
         const uint32_t w2 = has_seg(BW, 2) ? r2[(j * 2 + h) * 32 + lane] : 0u;
         const uint32_t w1 = has_seg(BW, 1) ? r1[j * 32 + lane] : 0u;
         uint32_t pat[8];
-        unpack16<E_BITS>(w4a, w4b, w2, w1, h, pat);
+        unpack16_any<E_BITS, M_BITS>(w4a, w4b, w2, w1, h, pat);
 #pragma unroll
         for (int kk = 0; kk < 2; kk++)
 #pragma unroll
@@ -212,10 +212,11 @@ cudaError_t launch_prepack(int e_bits, int m_bits, cudaStream_t stream, const vo
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
     const uint8_t* in = static_cast<const uint8_t*>(unpacked);
     uint8_t* out = static_cast<uint8_t*>(packed);
-    if (e_bits == 3)
-        prepack_kernel<6><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K);
-    else
-        prepack_kernel<5><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K);
+    switch (1 + e_bits + m_bits) {
+        case 4:  prepack_kernel<4><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K); break;
+        case 5:  prepack_kernel<5><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K); break;
+        default: prepack_kernel<6><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K); break;
+    }
     return cudaGetLastError();
 }
 
@@ -228,10 +229,7 @@ cudaError_t launch_quantize_prepack(int e_bits, int m_bits, cudaStream_t stream,
     const size_t blocks = (M / kRowsPerBlock) * ((kblocks + kChunkKBlocks - 1) / kChunkKBlocks);
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
     uint8_t* out = static_cast<uint8_t*>(packed);
-    if (e_bits == 3)
-        quantize_prepack_kernel<6><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(weights, scales, out, (uint32_t)M, (uint32_t)K);
-    else
-        quantize_prepack_kernel<5><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(weights, scales, out, (uint32_t)M, (uint32_t)K);
+    FPX_DISPATCH_FORMAT(e_bits, m_bits, (quantize_prepack_kernel<kE, kM><<<(unsigned)blocks, kPrepackThreads, 0, stream>>>(weights, scales, out, (uint32_t)M, (uint32_t)K)));
     return cudaGetLastError();
 }
 
@@ -243,10 +241,7 @@ cudaError_t launch_dequant_unpacked(int e_bits, int m_bits, cudaStream_t stream,
     const size_t blocks = (groups + 255) / 256;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
     const uint8_t* in = static_cast<const uint8_t*>(unpacked);
-    if (e_bits == 3)
-        dequant_unpacked_kernel<6><<<(unsigned)blocks, 256, 0, stream>>>(in, scales, out, (uint32_t)M, (uint32_t)K);
-    else
-        dequant_unpacked_kernel<5><<<(unsigned)blocks, 256, 0, stream>>>(in, scales, out, (uint32_t)M, (uint32_t)K);
+    FPX_DISPATCH_FORMAT(e_bits, m_bits, (dequant_unpacked_kernel<kE, kM><<<(unsigned)blocks, 256, 0, stream>>>(in, scales, out, (uint32_t)M, (uint32_t)K)));
     return cudaGetLastError();
 }
 
@@ -259,10 +254,7 @@ cudaError_t launch_dequant_packed(int e_bits, int m_bits, cudaStream_t stream, c
     const size_t blocks = (units + 3) / 4;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
     const uint8_t* in = static_cast<const uint8_t*>(packed);
-    if (e_bits == 3)
-        dequant_packed_kernel<6><<<(unsigned)blocks, 128, 0, stream>>>(in, scales, out, (uint32_t)M, (uint32_t)K);
-    else
-        dequant_packed_kernel<5><<<(unsigned)blocks, 128, 0, stream>>>(in, scales, out, (uint32_t)M, (uint32_t)K);
+    FPX_DISPATCH_FORMAT(e_bits, m_bits, (dequant_packed_kernel<kE, kM><<<(unsigned)blocks, 128, 0, stream>>>(in, scales, out, (uint32_t)M, (uint32_t)K)));
     return cudaGetLastError();
 }
 

@@ -3,6 +3,8 @@
 FPx code = [sign | E exponent bits | M mantissa bits], no inf/NaN.  The reference dequantises a code by
 moving it into fp16 bit positions (sign kept, the rest shifted right by 5-E) and multiplying by
 2^(16 - 2^(E-1)) (fp6_llm/csrc/utils/weight_dequant.h:30-43), so e3m2 covers 0..28 and e2m2 covers 0..7.
+The reference dispatches e3m2 and e2m2; its templates are generic, and this library also takes e2m1 (4-bit, 0..6),
+e3m1 (5-bit, 0..24) and e2m3 (6-bit, 0..7.5).
 
 The *unpacked* weight tensor of the reference is int32 [OC, IC*bw/32]; viewed as bytes each row is an
 MSB-first stream of bw-bit codes (fp6_llm/csrc/utils/common.h:9-17, fp6_llm/csrc/utils/weight_quant.h:74-76).
@@ -14,7 +16,7 @@ from __future__ import annotations
 
 import torch
 
-SUPPORTED = ((3, 2), (2, 2))
+SUPPORTED = ((3, 2), (2, 2), (2, 1), (3, 1), (2, 3))
 
 
 def bit_width(e_bits: int, m_bits: int) -> int:
@@ -23,7 +25,7 @@ def bit_width(e_bits: int, m_bits: int) -> int:
 
 def check_format(e_bits: int, m_bits: int) -> None:
     if (e_bits, m_bits) not in SUPPORTED:
-        raise ValueError(f"unsupported FPx format e{e_bits}m{m_bits}; supported: e3m2, e2m2")
+        raise ValueError(f"unsupported FPx format e{e_bits}m{m_bits}; supported: e3m2, e2m2, e2m1, e3m1, e2m3")
 
 
 def magnitudes(e_bits: int, m_bits: int) -> torch.Tensor:
@@ -89,11 +91,12 @@ def unpack_codes(w_unpacked: torch.Tensor, e_bits: int, m_bits: int) -> torch.Te
 
 def synth_layer(oc: int, ic: int, e_bits: int, m_bits: int, seed: int, device="cpu", std: float = 0.02):
     """Seeded stand-in for a checkpoint layer: fp16 N(0, std) weights, per-row scale max|w| / (28 for e3m2,
-    7.5 for e2m2), round-to-nearest codes.  Returns (unpacked int32 [OC, IC*bw/32], scale fp16 [OC])."""
+    7.5 for e2m2, the largest magnitude for the other formats), round-to-nearest codes.  Returns (unpacked int32 [OC, IC*bw/32], scale fp16 [OC])."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     w = (torch.randn(oc, ic, generator=gen, device=device, dtype=torch.float32) * std).to(torch.float16)
-    denom = 28.0 if e_bits == 3 else 7.5
+    # the row maximum lands on the largest magnitude; e2m2 keeps the 7.5 the benchmark configuration names (it saturates to 7)
+    denom = 7.5 if (e_bits, m_bits) == (2, 2) else float(magnitudes(e_bits, m_bits)[-1])
     scale = (w.abs().amax(dim=1).to(torch.float32) / denom).to(torch.float16)
     scale = torch.where(scale == 0, torch.ones_like(scale), scale)
     codes = quantize_rtn(w, scale, e_bits, m_bits)

@@ -131,7 +131,11 @@ static uint32_t interleave_word(uint32_t in, int seg_w) {
     return out;
 }
 
-static int supported(int e, int m) { return (e == 3 && m == 2) || (e == 2 && m == 2); }
+/* The reference's templates take any code narrower than 8 bits (weight_prepacking.h:124-128, weight_dequant.h:14-15);
+ * its run-time dispatch knows e3m2 and e2m2.  Restated here for those two and for e2m1, e3m1 and e2m3. */
+static int supported(int e, int m) {
+    return (m == 2 && (e == 3 || e == 2)) || (m == 1 && (e == 2 || e == 3)) || (m == 3 && e == 2);
+}
 
 /*
  * weight_prepacking.h:118-196.  `in`: rows x (cols*bw/8) bytes, each row an

@@ -27,7 +27,8 @@ def main():
     oracle.build(ref_root)
     assert oracle.have_ref(), "oracle/_ref was not built: reference tree missing?"
     rng = np.random.default_rng(20240607)
-    for e, m in ((3, 2), (2, 2)):
+    # the two formats the reference dispatches, then three more instantiations of its templates (same generator, appended)
+    for e, m in ((3, 2), (2, 2), (2, 1), (3, 1), (2, 3)):
         bw = 1 + e + m
         rows, cols = 256, 192
         w = rng.integers(-2**31, 2**31, size=(rows, cols * bw // 32), dtype=np.int64).astype(np.int32)
@@ -45,6 +46,7 @@ def main():
         np.savez_compressed(os.path.join(HERE, f"all_codes_e{e}m{m}.npz"), unpacked=w, scale=scale, codes=codes.astype(np.uint8),
                             packed=oracle.ref_prepack(w, e, m), dequant=oracle.ref_dequant(w, scale, e, m))
 
+    ref_root = ref_root or oracle._find_reference()
     src = open(os.path.join(ref_root, "fp6_llm", "__init__.py")).read()
     src = "\n".join(line for line in src.splitlines() if not re.match(r"\s*from fp6_llm_cuda import", line))
     ns = {}

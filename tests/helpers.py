@@ -4,7 +4,8 @@ import os
 import numpy as np
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-FORMATS = ((3, 2), (2, 2))
+FORMATS = ((3, 2), (2, 2))                       # what the reference dispatches
+ALL_FORMATS = FORMATS + ((2, 1), (3, 1), (2, 3))   # plus the other instantiations of its templates that this library takes
 KAT_ONES_E3M2 = (806142768, 3274706115, 214118412)                          # reference tests/python/kernel_test_fpx.py:124-131
 KAT_ONES_E2M2 = (272762913, 1107829124, 136414224, 562303042, 2215657992)   # reference tests/python/kernel_test_fpx.py:92-107
 

@@ -57,12 +57,22 @@ int harness_unpack(int e_bits, int m_bits, uint16_t* out_bits, const uint8_t* pa
                         uint32_t w2 = has_seg(bw, 2) ? r2[(j * 2 + h) * 32 + lane] : 0u;
                         uint32_t w1 = has_seg(bw, 1) ? r1[j * 32 + lane] : 0u;
                         uint32_t pat[8];
-                        if (e_bits == 3) unpack16<3>(w4a, w4b, w2, w1, h, pat); else unpack16<2>(w4a, w4b, w2, w1, h, pat);
-                        // the multiply-based sequence of the GEMM's inner loop must give the same registers
                         uint32_t pat2[8];
                         const UnpackMul km = unpack_mul_values(h);
-                        if (e_bits == 3) unpack16_mul<3>(w4a, w4b, w2, w1, km, pat2); else unpack16_mul<2>(w4a, w4b, w2, w1, km, pat2);
-                        for (int i = 0; i < 8; i++) if (pat[i] != pat2[i]) return -2;
+                        if (m_bits == 2 && e_bits == 3) {
+                            unpack16<3>(w4a, w4b, w2, w1, h, pat);
+                            unpack16_mul<3>(w4a, w4b, w2, w1, km, pat2);      // the GEMM's multiply-based sequence: same registers
+                            for (int i = 0; i < 8; i++) if (pat[i] != pat2[i]) return -2;
+                            unpack16_generic<3, 2>(w4a, w4b, w2, w1, h, pat2);   // and so must the general sequence
+                        } else if (m_bits == 2 && e_bits == 2) {
+                            unpack16<2>(w4a, w4b, w2, w1, h, pat);
+                            unpack16_mul<2>(w4a, w4b, w2, w1, km, pat2);
+                            for (int i = 0; i < 8; i++) if (pat[i] != pat2[i]) return -2;
+                            unpack16_generic<2, 2>(w4a, w4b, w2, w1, h, pat2);
+                        } else if (e_bits == 2 && m_bits == 1) { unpack16_any<2, 1>(w4a, w4b, w2, w1, h, pat); unpack16_generic<2, 1>(w4a, w4b, w2, w1, h, pat2); }
+                        else if (e_bits == 3 && m_bits == 1) { unpack16_any<3, 1>(w4a, w4b, w2, w1, h, pat); unpack16_generic<3, 1>(w4a, w4b, w2, w1, h, pat2); }
+                        else { unpack16_any<2, 3>(w4a, w4b, w2, w1, h, pat); unpack16_generic<2, 3>(w4a, w4b, w2, w1, h, pat2); }
+                        for (int i = 0; i < 8; i++) if (pat[i] != pat2[i]) return -3;
                         for (int kk = 0; kk < 2; kk++)
                             for (int i = 0; i < 4; i++) v[kk][4 * j + i] = pat[4 * kk + i];
                     }
@@ -153,7 +163,7 @@ int harness_check_plan(uint32_t mode, uint32_t m_tiles, uint32_t n_tiles, uint32
 
 
 // Codes of n quotients, as the fused quantise + pack kernel computes them.
-void harness_quantize(int e_bits, const float* q, int n, unsigned char* codes) {
-    for (int i = 0; i < n; i++) codes[i] = (unsigned char)fpx::quantize_rtn_code(e_bits, q[i]);
+void harness_quantize(int e_bits, int m_bits, const float* q, int n, unsigned char* codes) {
+    for (int i = 0; i < n; i++) codes[i] = (unsigned char)fpx::quantize_rtn_code(e_bits, m_bits, q[i]);
 }
 }

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import FORMATS, GOLDEN, KAT_ONES_E2M2, KAT_ONES_E3M2
+from helpers import ALL_FORMATS, FORMATS, GOLDEN, KAT_ONES_E2M2, KAT_ONES_E3M2
 
 
 def test_value_tables():
@@ -23,7 +23,7 @@ def test_pack_codes_known_answer_words():
     assert w[0, :5].numpy().astype(np.uint32).tolist() == list(KAT_ONES_E2M2)
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 def test_pack_unpack_roundtrip_and_values(oracle_mod, e, m):
     from fp6_llm_b200.formats import code_values, pack_codes, random_codes_layer, unpack_codes
     w, s = random_codes_layer(128, 192, e, m, seed=4, scale_lo=0.01, scale_hi=1.0)
@@ -34,7 +34,7 @@ def test_pack_unpack_roundtrip_and_values(oracle_mod, e, m):
     assert torch.equal(got.view(torch.int16), expect.view(torch.int16))
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 def test_quantizer_nearest_even_and_saturation(e, m):
     from fp6_llm_b200.formats import magnitudes, quantize_rtn
     mag = magnitudes(e, m)

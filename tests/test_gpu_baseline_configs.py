@@ -81,6 +81,18 @@ def test_scales_beyond_the_fp16_range_of_scale_times_bias(oracle_mod, e, m, bs, 
     _check(oracle_mod, f.linear_forward_eXmY_cuda(e, m, x, packed, s, split_k), truth)
 
 
+@pytest.mark.parametrize("e,m", [(2, 1), (3, 1), (2, 3)])
+@pytest.mark.parametrize("oc,ic,bs,split_k", [(512, 1024, 1, 0), (768, 4096, 16, 0), (512, 2048, 40, 3), (256, 8192, 130, 0), (512, 1024, 300, 1)])
+def test_other_formats_of_the_reference_templates(oracle_mod, e, m, oc, ic, bs, split_k):
+    """e2m1 (4-bit), e3m1 (5-bit) and e2m3 (6-bit): formats the reference's packer and dequantiser templates cover although
+    its GEMM launcher does not; same oracle recipe, same tolerances, every tile width."""
+    import fp6_llm_b200 as f
+    packed, s, x, truth = _oracle_case(oracle_mod, e, m, oc, ic, bs, seed=oc + bs + e)
+    _check(oracle_mod, f.linear_forward_eXmY_cuda(e, m, x, packed, s, split_k), truth)
+    packed, s, x, truth = _oracle_case(oracle_mod, e, m, oc, ic, bs, seed=bs + e, scale_lo=0.01, scale_hi=0.1)   # uniformly random codes
+    _check(oracle_mod, f.linear_forward_eXmY_cuda(e, m, x, packed, s, split_k), truth)
+
+
 # ------------------------------------------------------------------------------------------------ full layer shapes
 _FULL = {"qkv": (10240, 8192), "o": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}
 

@@ -8,7 +8,7 @@ import subprocess
 import numpy as np
 import pytest
 
-from helpers import FORMATS, random_unpacked
+from helpers import ALL_FORMATS, random_unpacked
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -21,7 +21,7 @@ def harness(tmp_path_factory):
     return ctypes.CDLL(so)
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 @pytest.mark.parametrize("rows,cols", [(128, 64), (256, 192), (384, 320)])
 def test_prepack_gather_matches_oracle(harness, oracle_mod, e, m, rows, cols):
     rng = np.random.default_rng(rows + cols + e)
@@ -31,7 +31,7 @@ def test_prepack_gather_matches_oracle(harness, oracle_mod, e, m, rows, cols):
     assert np.array_equal(out, oracle_mod.prepack(w, e, m))
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 @pytest.mark.parametrize("rows,cols", [(128, 64), (256, 256)])
 def test_gemm_unpack_registers(harness, oracle_mod, e, m, rows, cols):
     rng = np.random.default_rng(rows * 3 + cols + e)
@@ -76,7 +76,7 @@ def test_work_plans_cover_every_unit_once(harness):
     assert n > 1000
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 def test_quantiser_matches_the_tensor_quantiser(harness, e, m):
     """The scalar round-to-nearest routine of the fused quantise + pack kernel against formats.quantize_rtn, on random
     quotients, on every magnitude, on every exact tie between neighbours, beyond the largest magnitude and on signed
@@ -91,7 +91,7 @@ def test_quantiser_matches_the_tensor_quantiser(harness, e, m):
                    torch.tensor([0.0, -0.0, 1e-30, -1e-30, 1e6, -1e6, float(mag[-1]) * 1.0001])]).float().contiguous()
     expect = quantize_rtn(q[None, :], torch.ones(1), e, m)[0].numpy()
     got = np.zeros(q.numel(), np.uint8)
-    harness.harness_quantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    harness.harness_quantize.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
     harness.harness_quantize.restype = None
-    harness.harness_quantize(e, ctypes.c_void_p(q.numpy().ctypes.data), q.numel(), ctypes.c_void_p(got.ctypes.data))
+    harness.harness_quantize(e, m, ctypes.c_void_p(q.numpy().ctypes.data), q.numel(), ctypes.c_void_p(got.ctypes.data))
     assert np.array_equal(got, expect)

@@ -3,10 +3,10 @@ words of the reference's tests, and the committed fixtures that the reference co
 import numpy as np
 import pytest
 
-from helpers import FORMATS, kat_ones, load_golden, random_unpacked
+from helpers import ALL_FORMATS, FORMATS, kat_ones, load_golden, random_unpacked
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 def test_golden_prepack_and_dequant(oracle_mod, e, m):
     for name in (f"prepack_dequant_e{e}m{m}.npz", f"all_codes_e{e}m{m}.npz"):
         g = load_golden(name)
@@ -15,7 +15,7 @@ def test_golden_prepack_and_dequant(oracle_mod, e, m):
         assert np.array_equal(got.view(np.uint16), g["dequant"].view(np.uint16))
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 def test_all_codes_fixture_values(oracle_mod, e, m):
     """The all-codes fixture dequantises to the closed-form value table (scale 1)."""
     import torch
@@ -36,7 +36,7 @@ def test_known_answer_all_ones(oracle_mod, e, m):
     assert np.all(oracle_mod.linear(x, w, np.ones(64, np.float16), e, m) == 128.0)
 
 
-@pytest.mark.parametrize("e,m", FORMATS)
+@pytest.mark.parametrize("e,m", ALL_FORMATS)
 @pytest.mark.parametrize("rows,cols", [(64, 64), (256, 128), (192, 320)])
 def test_against_compiled_reference(oracle_mod, e, m, rows, cols):
     if not oracle_mod.have_ref():
