@@ -28,7 +28,7 @@ C_SYMBOLS = (
     "fp6b200_dequant", "fp6b200_dequant_host", "fp6b200_dequant_packed", "fp6b200_splitk_reduce",
     "fp6b200_device_status", "fp6b200_linear_static_scratch", "fp6b200_static_scratch_bytes",
     "fp6b200_linear_gather", "fp6b200_set_option", "fp6b200_get_option", "fp6b200_quantize_prepack",
-    "fp6b200_linear_host_io_batch", "fp6b200_kernel_launches",
+    "fp6b200_linear_host_io_batch", "fp6b200_kernel_launches", "fp6b200_linear_ex",
 )
 
 
@@ -90,6 +90,8 @@ def lib() -> ctypes.CDLL:
     L.fp6b200_error_string.argtypes = [ci]
     L.fp6b200_linear.restype = ci
     L.fp6b200_linear.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, ci]
+    L.fp6b200_linear_ex.restype = ci
+    L.fp6b200_linear_ex.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, ci, vp, ci]
     L.fp6b200_linear_host_io.restype = ci
     L.fp6b200_linear_host_io.argtypes = [ci, ci, vp, vp, vp, vp, sz, sz, sz, ci]
     L.fp6b200_linear_host_io_batch.restype = ci

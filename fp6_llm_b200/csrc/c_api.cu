@@ -137,6 +137,18 @@ int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_pack
                             static_cast<__half*>(out), M, N, K, workspace, split_k, status);
 }
 
+int fp6b200_linear_ex(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales, const void* act,
+                      void* out, size_t M, size_t N, size_t K, float* workspace, int split_k, const void* bias, int activation) {
+    int* status = status_ptr();
+    if (!status) return cudaErrorInitializationError;
+    fpx::Epilogue epi;
+    epi.bias = static_cast<const __half*>(bias);
+    epi.activation = activation;
+    return fpx::launch_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_packed,
+                            static_cast<const __half*>(scales), static_cast<const __half*>(act),
+                            static_cast<__half*>(out), M, N, K, workspace, split_k, status, nullptr, &epi);
+}
+
 int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weight_shard, const void* scales_shard,
                           const void* act, void* const* out_peers, void* const* flag_peers, void* epoch_counter, int world,
                           int rank, size_t out_rows, size_t row0, size_t M, size_t N, size_t K, float* workspace,
@@ -344,7 +356,7 @@ int fp6b200_dequant_packed(int e_bits, int m_bits, void* stream, const void* pac
 int fp6b200_splitk_reduce(void* stream, void* out_dev, const float* partials_dev, size_t elems, int split_k) {
     if (!out_dev || !partials_dev || elems == 0 || elems % 4 || split_k < 1) return cudaErrorInvalidValue;
     return fpx::launch_splitk_reduce(static_cast<cudaStream_t>(stream), static_cast<__half*>(out_dev), partials_dev,
-                                     elems, split_k);
+                                     elems, split_k, false, 0, nullptr);
 }
 
 int fp6b200_device_status(int* code) {

@@ -170,6 +170,9 @@ __device__ unsigned long long g_stamp[160][16];   // global-timer stamps (ns) of
 
 constexpr uint32_t kMaxGrid = 256;   // CTAs the fix-up kernel's slot list can hold
 
+// silu(gate) * up in fp32
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
+
 struct Params {
     const uint8_t* weight;
     const uint8_t* region[3];   // start of the 1-bit, 2-bit and 4-bit regions of the packed weights
@@ -177,6 +180,8 @@ struct Params {
     OutTargets out;             // where finished fp16 tiles go (this GPU's buffer, or every rank's)
     uint32_t weights_static;    // the packed weights are not written by earlier work of the stream: read them at once
     UnpackMul mul[2];           // unpack16_mul's multipliers for h = 0, 1 (parameters so that they stay multiplications)
+    const __half* bias;         // per-row addend, or nullptr
+    uint32_t activation;        // kActNone / kActSiluMul (rows in gate/up pairs)
     float* workspace;
     uint32_t M, N, K;
     WorkPlan plan;
@@ -428,6 +433,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             const uint32_t row = m_tile * kTileM + row_in_tile;
             // the accumulator holds sum(x * pattern); pattern = code value / 2^bias, so scale by 2^bias * scale[row] here, in fp32
             const float row_scale = __half2float(p.scales[row]) * (float)(1u << (16 - (1 << (E_BITS - 1))));
+            const float row_bias = p.bias ? __half2float(p.bias[row]) : 0.0f;   // added where a tile is finished: here, or in the fix-up / reduction
             if (!PROF_WAIT(5, ptx::mbar_wait_warp(acc_full, nseg & 1u, abort_word, kErrAccFull))) { ok = false; break; }
             if (threadIdx.x == 0) PROF_STAMP(7);
             ptx::tc_fence_after_sync();
@@ -452,14 +458,29 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     }
                 if (seg.out_kind == kOutDirect) {
 #pragma unroll
-                    for (int u = 0; u < CH; u++) f[u] *= row_scale;
-                    const size_t first = (size_t)n0 * p.out.ld + p.out.row0 + row;
-#pragma unroll 1
-                    for (uint32_t r = 0; r < p.out.count; r++) {   // one target, or the buffer of every rank
-                        __half* dst = p.out.ptr[r] + first;
+                    for (int u = 0; u < CH; u++) f[u] = f[u] * row_scale + row_bias;
+                    if (p.activation == kActSiluMul) {
+                        // rows 2c (gate) and 2c+1 (up) sit in neighbouring lanes: the even lane computes and stores channel c
 #pragma unroll
-                        for (int u = 0; u < CH; u++)
-                            if (n0 + u < p.N) dst[(size_t)u * p.out.ld] = __float2half_rn(f[u]);
+                        for (int u = 0; u < CH; u++) {
+                            const float up = __shfl_xor_sync(0xffffffffu, f[u], 1);
+                            f[u] = silu_mul(f[u], up);
+                        }
+                        if ((lane & 1) == 0) {
+                            __half* dst = p.out.ptr[0] + (size_t)n0 * p.out.ld + p.out.row0 + (row >> 1);
+#pragma unroll
+                            for (int u = 0; u < CH; u++)
+                                if (n0 + u < p.N) dst[(size_t)u * p.out.ld] = __float2half_rn(f[u]);
+                        }
+                    } else {
+                        const size_t first = (size_t)n0 * p.out.ld + p.out.row0 + row;
+#pragma unroll 1
+                        for (uint32_t r = 0; r < p.out.count; r++) {   // one target, or the buffer of every rank
+                            __half* dst = p.out.ptr[r] + first;
+#pragma unroll
+                            for (int u = 0; u < CH; u++)
+                                if (n0 + u < p.N) dst[(size_t)u * p.out.ld] = __float2half_rn(f[u]);
+                        }
                     }
                 } else if (seg.out_kind == kOutSplitPartial) {
                     float* dst = p.workspace + ((size_t)seg.out_index * p.N + n0) * p.M + row;
@@ -610,7 +631,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
 // Split-K reduction: out[i] = rn_half(sum over splits, ascending, fp32), the semantics of the
 // reference's SplitK_Reduction (fp6_llm/csrc/include/kernel_reduction.cuh:28-47).
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__ out, const float* __restrict__ partials,
-                                                            size_t elems, int split_k) {
+                                                            size_t elems, int split_k, uint32_t rows,
+                                                            const __half* __restrict__ bias, int activation) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op unless launched with programmatic serialisation
     if (i >= elems) return;
@@ -618,6 +640,16 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
     for (int s = 0; s < split_k; s++) {
         const float4 v = *reinterpret_cast<const float4*>(partials + (size_t)s * elems + i);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias) {   // four consecutive rows of one token (rows is a multiple of 4)
+        const uint32_t m = (uint32_t)(i % rows);
+        acc.x += __half2float(bias[m]); acc.y += __half2float(bias[m + 1]);
+        acc.z += __half2float(bias[m + 2]); acc.w += __half2float(bias[m + 3]);
+    }
+    if (activation == kActSiluMul) {   // two gate/up pairs -> two output channels of out[N][rows / 2]
+        const __half2 r = __floats2half2_rn(silu_mul(acc.x, acc.y), silu_mul(acc.z, acc.w));
+        *reinterpret_cast<__half2*>(out + i / 2) = r;
+        return;
     }
     __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
     uint2 packed;
@@ -638,7 +670,7 @@ constexpr uint64_t kFixupCostUnits = 20;   // the fix-up launch and its dependen
 constexpr uint64_t kMinUnitsPerCta = 8;   // a CTA is not started for fewer 64-K blocks than this (two 256-K stages)
 __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
                                                                          uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan,
-                                                                         int early_trigger) {
+                                                                         int early_trigger, const __half* __restrict__ bias, int activation) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
@@ -682,12 +714,22 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __
             const float4 v = *reinterpret_cast<const float4*>(base + part_slot[i] * slot_stride);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
-        uint2 packed;
-        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-        packed.y = *reinterpret_cast<uint32_t*>(&hi);
-        const size_t at = (size_t)n * out.ld + out.row0 + m_tile * kTileM + row4;
-        for (uint32_t t = 0; t < out.count; t++) *reinterpret_cast<uint2*>(out.ptr[t] + at) = packed;
+        const uint32_t m0 = m_tile * kTileM + row4;
+        if (bias) {
+            acc.x += __half2float(bias[m0]); acc.y += __half2float(bias[m0 + 1]);
+            acc.z += __half2float(bias[m0 + 2]); acc.w += __half2float(bias[m0 + 3]);
+        }
+        if (activation == kActSiluMul) {   // two gate/up pairs -> two output channels
+            const __half2 r2 = __floats2half2_rn(silu_mul(acc.x, acc.y), silu_mul(acc.z, acc.w));
+            *reinterpret_cast<__half2*>(out.ptr[0] + (size_t)n * out.ld + out.row0 + (m0 >> 1)) = r2;
+        } else {
+            __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            const size_t at = (size_t)n * out.ld + out.row0 + m0;
+            for (uint32_t t = 0; t < out.count; t++) *reinterpret_cast<uint2*>(out.ptr[t] + at) = packed;
+        }
     }
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(12);
 }
@@ -883,7 +925,10 @@ size_t gemm_auto_workspace_bytes(size_t N) {
 }
 
 cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k,
-                                 bool after_gemm) {
+                                 bool after_gemm, size_t rows, const Epilogue* epilogue) {
+    const __half* bias = epilogue ? epilogue->bias : nullptr;
+    const int activation = epilogue ? epilogue->activation : kActNone;
+    if ((bias || activation != kActNone) && (rows == 0 || rows % 4 != 0 || elems % rows != 0)) return cudaErrorInvalidValue;
     const size_t threads = (elems + 3) / 4;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
@@ -894,7 +939,7 @@ cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* 
     attr[0].val.programmaticStreamSerializationAllowed = after_gemm ? 1 : 0;   // overlap the launch with the GEMM's tail
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, out, partials, elems, split_k);
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, out, partials, elems, split_k, (uint32_t)rows, bias, activation);
 }
 
 static std::atomic<int> g_weights_static{0};
@@ -906,8 +951,13 @@ int programmatic_launch() { return g_programmatic_launch.load(); }
 
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
-                        int* status, const OutTargets* targets) {
+                        int* status, const OutTargets* targets, const Epilogue* epilogue) {
     if (!format_supported(e_bits, m_bits)) return cudaErrorInvalidValue;
+    const __half* bias = epilogue ? epilogue->bias : nullptr;
+    const int activation = epilogue ? epilogue->activation : kActNone;
+    if (activation != kActNone && activation != kActSiluMul) return cudaErrorInvalidValue;
+    if (activation != kActNone && targets) return cudaErrorInvalidValue;   // the fused exchange stores plain rows only
+    if (bias && (reinterpret_cast<uintptr_t>(bias) & 1)) return cudaErrorMisalignedAddress;
     OutTargets where;
     if (targets) {
         where = *targets;
@@ -921,7 +971,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     } else {
         where.ptr[0] = out;
         where.count = 1;
-        where.ld = (uint32_t)M;
+        where.ld = (uint32_t)(activation == kActSiluMul ? M / 2 : M);
         where.row0 = 0;
     }
     if (M == 0 || M % 256 != 0 || K == 0 || K % 64 != 0 || N == 0 || split_k < 0 || split_k > 65535)
@@ -953,6 +1003,8 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     prm.weights_static = (uint32_t)weights_static();
     prm.mul[0] = unpack_mul_values(0);
     prm.mul[1] = unpack_mul_values(1);
+    prm.bias = bias;
+    prm.activation = (uint32_t)activation;
     prm.M = (uint32_t)M;
     prm.N = (uint32_t)N;
     prm.K = (uint32_t)K;
@@ -974,9 +1026,9 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         const int early = programmatic_launch() ? 1 : 0;
-        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan, early);
+        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan, early, bias, activation);
     }
-    if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true);
+    if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true, M, epilogue);
     return cudaSuccess;
 }
 

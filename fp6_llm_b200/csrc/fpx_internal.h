@@ -34,18 +34,30 @@ struct OutTargets {
     uint32_t row0;
 };
 
+// What happens to an output element between the fp32 accumulator and the fp16 store (after the row scale):
+//   bias        per-row fp16 addend [M], or nullptr;
+//   activation  kActNone, or kActSiluMul: rows come in pairs (2c = gate, 2c+1 = up) and the layer's output channel c is
+//               silu(gate) * up, so the output is [N][M / 2].
+enum : int { kActNone = 0, kActSiluMul = 1 };
+struct Epilogue {
+    const __half* bias;
+    int activation;
+};
+
 // GEMM (+ split-K reduction when split_k > 1).  All pointers are device pointers.  targets == nullptr: the result
-// goes to out[N][M]; otherwise out is ignored (split_k must then be 0 or 1).
+// goes to out[N][M] (out[N][M / 2] with kActSiluMul); otherwise out is ignored (split_k must then be 0 or 1, and no
+// activation).  epilogue == nullptr: plain layer.
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
-                        int* status, const OutTargets* targets = nullptr);
+                        int* status, const OutTargets* targets = nullptr, const Epilogue* epilogue = nullptr);
 // Cross-GPU arrival barrier that ends a sharded layer: tells every peer that this rank's stores into its output
 // buffer are complete and waits (bounded) for the same word from every peer.  flag_peers[r] = rank r's flag array
 // (one 32-bit word per rank) as mapped here; epoch_counter = this rank's own call counter in device memory.
 cudaError_t launch_gather_barrier(cudaStream_t stream, uint32_t* const* flag_peers, int world, int rank,
                                   uint32_t* epoch_counter, int* status);
+// out[n][m] = rn_half(epilogue(sum over splits of partials[s][n][m])); rows = M (needed for the bias and the pairing).
 cudaError_t launch_splitk_reduce(cudaStream_t stream, __half* out, const float* partials, size_t elems, int split_k,
-                                 bool after_gemm = false);
+                                 bool after_gemm = false, size_t rows = 0, const Epilogue* epilogue = nullptr);
 // Process-wide promise that packed weights are never written by work still in flight on the stream of a GEMM that
 // reads them; the GEMM then requests them before the previous kernel of its stream has completed.  Off by default.
 void set_weights_static(int on);

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .formats import bit_width, check_format, magnitudes
-from .ops import linear_forward_eXmY_cuda, quantize_prepack_cuda
+from .ops import ACT_NONE, ACT_SILU_MUL, interleave_gate_up, linear_forward_ex, quantize_prepack_cuda
 
 
 class FPxLinear(torch.nn.Module):
@@ -52,10 +52,56 @@ class FPxLinear(torch.nn.Module):
         if x.dtype != torch.float16 or x.shape[-1] != self.in_features:
             raise ValueError(f"expected fp16 activations [..., {self.in_features}]")
         flat = x.reshape(-1, self.in_features).contiguous()
-        y = linear_forward_eXmY_cuda(self.e_bits, self.m_bits, flat, self.weight, self.scales, self.split_k)
-        if self.bias is not None:
-            y = y + self.bias
+        # the bias is added inside the kernel's fp32 epilogue, before the one rounding to fp16
+        y = linear_forward_ex(self.e_bits, self.m_bits, flat, self.weight, self.scales, self.split_k, self.bias, ACT_NONE)
         return y.reshape(*x.shape[:-1], self.out_features)
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, format=e{self.e_bits}m{self.m_bits}"
+
+
+class FPxGateUpLinear(torch.nn.Module):
+    """The first half of a LLaMA-style MLP in one launch: y = silu(x @ Wg^T + bg) * (x @ Wu^T + bu), with Wg and Wu held
+    as ONE prepacked FPx matrix whose rows alternate gate / up, so that the kernel's epilogue sees both values of an
+    output channel side by side and stores only the product ([..., C] instead of [..., 2C])."""
+
+    def __init__(self, packed: torch.Tensor, scales: torch.Tensor, bias: torch.Tensor | None = None, e_bits: int = 3,
+                 m_bits: int = 2, split_k: int = 0):
+        super().__init__()
+        check_format(e_bits, m_bits)
+        if packed.dtype != torch.int32 or packed.dim() != 2 or scales.dtype != torch.float16 or packed.shape[0] % 2:
+            raise ValueError("expected prepacked int32 weights [2C, IC/32*bw] (rows: gate, up, gate, up, ...) and fp16 scales [2C]")
+        if scales.numel() != packed.shape[0] or (bias is not None and bias.numel() != packed.shape[0]):
+            raise ValueError("scales and bias need one entry per weight row")
+        self.e_bits, self.m_bits, self.split_k = e_bits, m_bits, split_k
+        self.out_features = packed.shape[0] // 2
+        self.in_features = packed.shape[1] * 32 // bit_width(e_bits, m_bits)
+        self.register_buffer("weight", packed)
+        self.register_buffer("scales", scales)
+        self.register_buffer("bias", bias.to(torch.float16) if bias is not None else None)
+
+    @classmethod
+    def from_linears(cls, gate: torch.nn.Linear, up: torch.nn.Linear, e_bits: int = 3, m_bits: int = 2,
+                     split_k: int = 0) -> "FPxGateUpLinear":
+        """Quantise two (CUDA) torch.nn.Linear layers of equal shape into one interleaved, prepacked matrix."""
+        w = interleave_gate_up(gate.weight.detach().to(torch.float16), up.weight.detach().to(torch.float16))
+        if not w.is_cuda:
+            raise ValueError("the layers must live on a CUDA device: quantisation and packing run there")
+        scales = FPxLinear.row_scales(w, e_bits, m_bits)
+        packed = quantize_prepack_cuda(w, scales, e_bits, m_bits)
+        bias = None
+        if gate.bias is not None or up.bias is not None:
+            zero = torch.zeros(gate.out_features, dtype=torch.float16, device=w.device)
+            bias = interleave_gate_up(gate.bias.detach().half() if gate.bias is not None else zero,
+                                      up.bias.detach().half() if up.bias is not None else zero)
+        return cls(packed, scales, bias, e_bits, m_bits, split_k)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dtype != torch.float16 or x.shape[-1] != self.in_features:
+            raise ValueError(f"expected fp16 activations [..., {self.in_features}]")
+        flat = x.reshape(-1, self.in_features).contiguous()
+        y = linear_forward_ex(self.e_bits, self.m_bits, flat, self.weight, self.scales, self.split_k, self.bias, ACT_SILU_MUL)
+        return y.reshape(*x.shape[:-1], self.out_features)
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features} (gate and up fused), format=e{self.e_bits}m{self.m_bits}"

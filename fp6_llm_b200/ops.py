@@ -80,14 +80,10 @@ def _in_channels(weights: torch.Tensor, e_bits: int, m_bits: int) -> int:
 
 
 # ----------------------------------------------------------------------------- linear layer
-def linear_forward_eXmY_cuda(EXPONENT: int, MANTISSA: int, _in_feats: torch.Tensor, _weights: torch.Tensor,
-                             _scales: torch.Tensor, splitK: int = 1) -> torch.Tensor:
-    """Out[B, OC] = In[B, IC] @ dequant(W)[OC, IC]^T  (fp_eXmY_linear_forward_cuda,
-    fp6_llm/csrc/fp6_linear.cu:269-313).
+ACT_NONE, ACT_SILU_MUL = 0, 1
 
-    _in_feats  fp16 [B, IC] cuda;  _weights  int32 [OC, IC/32*(1+E+M)] cuda, prepacked;
-    _scales    fp16 [OC] cuda;     splitK >= 1 as in the reference, 0 = let the library choose.
-    Runs on the current torch stream (the reference uses the legacy default stream)."""
+
+def _linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK, bias, activation):
     _require_cuda()
     check_format(EXPONENT, MANTISSA)
     if _in_feats.dtype != torch.float16 or _scales.dtype != torch.float16 or _weights.dtype != torch.int32:
@@ -110,16 +106,53 @@ def linear_forward_eXmY_cuda(EXPONENT: int, MANTISSA: int, _in_feats: torch.Tens
         raise ValueError("scales must have OC elements")
     if splitK < 0:
         raise ValueError("splitK must be >= 0")
+    if activation not in (ACT_NONE, ACT_SILU_MUL):
+        raise ValueError("activation must be ACT_NONE or ACT_SILU_MUL")
+    if bias is not None and (bias.dtype != torch.float16 or bias.numel() != OC or bias.device != _in_feats.device
+                             or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous fp16 tensor with OC elements on the layer's device")
     dev = _in_feats.device
     L = _native.lib()
     with torch.cuda.device(dev):
         nbytes = L.fp6b200_workspace_bytes(OC, B, IC, splitK)
         ws = _workspace(dev, nbytes) if nbytes else None
-        out = torch.empty((B, OC), dtype=torch.float16, device=dev)
-        rc = L.fp6b200_linear(EXPONENT, MANTISSA, _stream_ptr(dev), _ptr(_weights), _ptr(_scales), _ptr(_in_feats),
-                              _ptr(out), OC, B, IC, _ptr(ws) if ws is not None else None, splitK)
+        out = torch.empty((B, OC // 2 if activation == ACT_SILU_MUL else OC), dtype=torch.float16, device=dev)
+        if bias is None and activation == ACT_NONE:
+            rc = L.fp6b200_linear(EXPONENT, MANTISSA, _stream_ptr(dev), _ptr(_weights), _ptr(_scales), _ptr(_in_feats),
+                                  _ptr(out), OC, B, IC, _ptr(ws) if ws is not None else None, splitK)
+        else:
+            rc = L.fp6b200_linear_ex(EXPONENT, MANTISSA, _stream_ptr(dev), _ptr(_weights), _ptr(_scales), _ptr(_in_feats),
+                                     _ptr(out), OC, B, IC, _ptr(ws) if ws is not None else None, splitK,
+                                     _ptr(bias) if bias is not None else None, activation)
     _native.check(rc, "fp6b200_linear")
     return out
+
+
+def linear_forward_eXmY_cuda(EXPONENT: int, MANTISSA: int, _in_feats: torch.Tensor, _weights: torch.Tensor,
+                             _scales: torch.Tensor, splitK: int = 1) -> torch.Tensor:
+    """Out[B, OC] = In[B, IC] @ dequant(W)[OC, IC]^T  (fp_eXmY_linear_forward_cuda,
+    fp6_llm/csrc/fp6_linear.cu:269-313).
+
+    _in_feats  fp16 [B, IC] cuda;  _weights  int32 [OC, IC/32*(1+E+M)] cuda, prepacked;
+    _scales    fp16 [OC] cuda;     splitK >= 1 as in the reference, 0 = let the library choose.
+    Runs on the current torch stream (the reference uses the legacy default stream)."""
+    return _linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK, None, ACT_NONE)
+
+
+def linear_forward_ex(EXPONENT: int, MANTISSA: int, _in_feats: torch.Tensor, _weights: torch.Tensor, _scales: torch.Tensor,
+                      splitK: int = 0, bias: torch.Tensor | None = None, activation: int = ACT_NONE) -> torch.Tensor:
+    """The layer with the epilogue fused into the kernel (C: fp6b200_linear_ex; the reference has no such entry): an fp16
+    bias [OC] added in fp32 before the one rounding, and optionally ACT_SILU_MUL, for which the weight rows come in
+    (gate, up) pairs - see :func:`interleave_gate_up` - and the result is [B, OC/2] = silu(gate) * up."""
+    return _linear(EXPONENT, MANTISSA, _in_feats, _weights, _scales, splitK, bias, activation)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Row order ACT_SILU_MUL expects: row 2c = gate[c], row 2c+1 = up[c].  Works on weights [C, IC], scales [C] or biases
+    [C]; apply it to the fp16 weights BEFORE quantising and packing (or to the unpacked code tensor before prepacking)."""
+    if gate.shape != up.shape:
+        raise ValueError("gate and up must have the same shape")
+    return torch.stack([gate, up], dim=1).reshape(gate.shape[0] * 2, *gate.shape[1:]).contiguous()
 
 
 def linear_forward_cuda(*args) -> torch.Tensor:

@@ -208,3 +208,87 @@ class ShardedFPxLinear:
         if self.exchange is not None:
             return self.exchange.linear(self, x, split_k)
         return gather_columns(self.forward_local(x, split_k), self.plan, self.rank, self.group)
+
+
+# ------------------------------------------------------------------------------------------------ IC-sharded (row-parallel)
+COL_UNIT = 64   # the kernel's K granularity (reference: fp6_llm/csrc/fp6_linear.cu:57)
+
+
+def plan_cols(in_channels: int, world_size: int) -> List[Tuple[int, int]]:
+    """[k0, k1) per rank: multiples of 64 input channels, as even as possible, earlier ranks take the remainder."""
+    if in_channels % COL_UNIT:
+        raise ValueError(f"IC={in_channels} is not a multiple of {COL_UNIT}")
+    units = in_channels // COL_UNIT
+    if world_size < 1 or units < world_size:
+        raise ValueError(f"cannot cut {units} column units over {world_size} ranks")
+    base, extra = divmod(units, world_size)
+    plan, k0 = [], 0
+    for r in range(world_size):
+        n = (base + (1 if r < extra else 0)) * COL_UNIT
+        plan.append((k0, k0 + n))
+        k0 += n
+    return plan
+
+
+def slice_unpacked_cols(w_unpacked: torch.Tensor, e_bits: int, m_bits: int, k0: int, k1: int) -> torch.Tensor:
+    """Input channels [k0, k1) of the UNPACKED int32 [OC, IC*bw/32] tensor (64 codes are 2*bw whole words, so a multiple
+    of 64 columns is a plain column slice); prepack the result to get the rank's weights.  The packed tensor cannot be
+    cut along K by slicing: every region interleaves the K blocks of a 64-row block."""
+    check_format(e_bits, m_bits)
+    bw = bit_width(e_bits, m_bits)
+    if k0 % COL_UNIT or k1 % COL_UNIT or not (0 <= k0 < k1 <= w_unpacked.shape[1] * 32 // bw):
+        raise ValueError("column shards must be multiples of 64 inside the matrix")
+    return w_unpacked[:, k0 * bw // 32: k1 * bw // 32].contiguous()
+
+
+def reduce_partials(partial: torch.Tensor, mode: str = "all_reduce", group=None) -> torch.Tensor:
+    """Sums the ranks' [B, OC] partial results.  "all_reduce": every rank gets the whole [B, OC].  "reduce_scatter": rank r
+    gets output channels [r*OC/world, (r+1)*OC/world) as [B, OC/world] (what a following column-parallel layer, or a
+    sequence-parallel region, consumes).  One collective either way; the sum is taken in the tensor's dtype (fp16), as
+    tensor-parallel inference engines do."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    if mode == "all_reduce":
+        out = partial.contiguous()
+        dist.all_reduce(out, group=group)
+        return out
+    if mode != "reduce_scatter":
+        raise ValueError("mode must be all_reduce or reduce_scatter")
+    batch, oc = partial.shape
+    if oc % world:
+        raise ValueError("OC must divide by the number of ranks for reduce_scatter")
+    send = partial.view(batch, world, oc // world).permute(1, 0, 2).contiguous()     # [world, B, OC/world]
+    out = partial.new_empty((batch, oc // world))
+    try:
+        dist.reduce_scatter_tensor(out, send, group=group)
+    except (RuntimeError, NotImplementedError):   # a backend without reduce-scatter (gloo): all-reduce, keep the own slab
+        dist.all_reduce(send, group=group)
+        out = send[dist.get_rank(group)].contiguous()
+    return out
+
+
+class RowParallelFPxLinear:
+    """One rank's part of an IC-sharded (row-parallel) FPx linear layer, the form the O and down projections take behind
+    a column-parallel layer: the rank holds the prepacked weights of its input channels [k0, k1) for ALL output channels
+    and receives the matching activation columns; the partial results are summed over the ranks by one collective.
+    The bias, if any, is added by rank 0 only (inside its kernel), so the sum carries it once."""
+
+    def __init__(self, packed_cols: torch.Tensor, scale: torch.Tensor, plan: Sequence[Tuple[int, int]], rank: int,
+                 e_bits: int = 3, m_bits: int = 2, bias: "torch.Tensor | None" = None, group=None, mode: str = "all_reduce"):
+        self.packed, self.scale, self.plan, self.rank = packed_cols, scale, list(plan), rank
+        self.e_bits, self.m_bits, self.group, self.mode = e_bits, m_bits, group, mode
+        self.bias = bias if rank == 0 else None
+        k0, k1 = self.plan[rank]
+        if packed_cols.shape[1] * 32 != (k1 - k0) * bit_width(e_bits, m_bits):
+            raise ValueError("packed shard does not match the column plan")
+
+    def forward_local(self, x_cols: torch.Tensor, split_k: int = 0) -> torch.Tensor:
+        from .ops import ACT_NONE, linear_forward_ex
+        return linear_forward_ex(self.e_bits, self.m_bits, x_cols, self.packed, self.scale, split_k, self.bias, ACT_NONE)
+
+    def forward(self, x_cols: torch.Tensor, split_k: int = 0) -> torch.Tensor:
+        """x_cols: this rank's activation columns [B, k1-k0] (the output slab of the column-parallel layer before it)."""
+        local = self.forward_local(x_cols, split_k)
+        if len(self.plan) == 1:
+            return local
+        return reduce_partials(local, self.mode, self.group)

@@ -42,6 +42,21 @@ int fp6b200_linear(int e_bits, int m_bits, void* stream, const void* weight_pack
                    const void* act, void* out, size_t M, size_t N, size_t K, float* workspace, int split_k);
 
 /*
+ * The layer with a fused epilogue (no counterpart in the reference, whose epilogue only converts and stores:
+ * fp6_llm/csrc/include/utils_core.cuh:105-130, kernel_matmul.cuh:183-190; inference engines add bias and the MLP's gating
+ * in separate kernels).  Between the fp32 accumulator (times the row scale) and the fp16 store:
+ *   bias        fp16 [M] device pointer, added in fp32, or NULL;
+ *   activation  FP6B200_ACT_NONE, or FP6B200_ACT_SILU_MUL: the weight rows come in pairs, row 2c = gate channel c and
+ *               row 2c+1 = up channel c (scales and bias in the same order), and the output is out[N][M/2] with
+ *               out[n][c] = silu(gate) * up - the gate+up projection of a LLaMA MLP in one launch.
+ * Everything else as fp6b200_linear.
+ */
+#define FP6B200_ACT_NONE 0
+#define FP6B200_ACT_SILU_MUL 1
+int fp6b200_linear_ex(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales, const void* act,
+                      void* out, size_t M, size_t N, size_t K, float* workspace, int split_k, const void* bias, int activation);
+
+/*
  * Same layer with HOST activations and output: copies act to the device, runs the layer, copies the
  * result back and synchronises.  Weights and scales stay resident on the device (they are parameters).
  * Stands in for the torch-level call fp_eXmY_linear_forward_cuda (fp6_llm/csrc/fp6_linear.cu:269-313)
