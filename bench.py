@@ -255,7 +255,7 @@ class Bench:
         for mdl in self.models:
             n_rep = min(64, max(self.replicas, -(-self.TARGET // mdl["widest"])))
             mdl["replicas"] = [ShardedFPxLinear(mdl["packed"] if r == 0 else mdl["packed"].clone(), mdl["scale"], mdl["plan"], rank, e, m,
-                                                exchange=exchange)
+                                                exchange=exchange, native=ctx.get("native", True))
                                for r in range(n_rep)]
         torch.cuda.synchronize(dev)
         self.acts = {(mdl["name"], bs): torch.randn(bs, mdl["ic"], device=dev, dtype=torch.float16)
@@ -344,7 +344,10 @@ class Bench:
         n = 0
         for mdl, bs in self.cases:
             r0, r1 = mdl["plan"][self.ctx["rank"]]
-            n += L.fp6b200_kernel_launches(r1 - r0, bs, mdl["ic"], self.split[(mdl["name"], bs)]) + (1 if with_barrier else 0)
+            if mdl["replicas"][0].use_native(bs, self.split[(mdl["name"], bs)]):
+                n += L.fp6b200_native_kernel_launches(r1 - r0, bs, mdl["ic"]) + (1 if with_barrier else 0)
+            else:
+                n += L.fp6b200_kernel_launches(r1 - r0, bs, mdl["ic"], self.split[(mdl["name"], bs)]) + (1 if with_barrier else 0)
         return n
 
     # -- every case alone
@@ -394,7 +397,8 @@ class Bench:
                      "us": round(us, 3), "tflops": round(fl / us / 1e6, 3),
                      "weight_gbs": round(mdl["oc"] * mdl["ic"] * self.bw / 8 / us / 1e3, 1),
                      "roofline_frac": round(t_roof / (us * 1e-6), 4),
-                     "bound": "hbm" if ab / (hbm_peak * 1e9) >= fl / world / (tc_peak * 1e12) else "tensor"}
+                     "bound": "hbm" if ab / (hbm_peak * 1e9) >= fl / world / (tc_peak * 1e12) else "tensor",
+                     "kernel": "fp6 tensor-core inputs" if mdl["replicas"][0].use_native(bs, self.split[key]) else "fp16 patterns"}
             if split_sweep and world == 1:
                 # the reference's explicit split-K scheme on this kernel: the given splits, and the library's K-aware choice
                 chosen = f.heuristic_split_k_b200(mdl["oc"], bs, mdl["ic"], ctx["sms"])
@@ -457,7 +461,7 @@ def run_ours(args):
     exchange = PeerExchange() if (world > 1 and args.exchange == "fused") else None
     ctx = {"dev": dev, "world": world, "rank": rank, "local_rank": local_rank, "dist": dist, "peaks": peaks(),
            "stream": torch.cuda.Stream(dev), "sms": torch.cuda.get_device_properties(dev).multi_processor_count,
-           "barrier": (lambda: dist.barrier()) if world > 1 else (lambda: None)}
+           "barrier": (lambda: dist.barrier()) if world > 1 else (lambda: None), "native": not args.no_native}
     hbm_peak, tc_peak, peak_kind = ctx["peaks"]
 
     e, m, layers, batches = select_cases(args)
@@ -605,6 +609,8 @@ def run_ours(args):
                        "l2": f"inputs larger than L2: {replicas_main} replica(s) of the layer set ({shard_main * replicas_main / 2**20:.0f} MiB) rotated so a buffer is re-read only after >= 512 MiB of other weights",
                        "launch": "whole step replayed as a CUDA graph; kernels launched programmatically (prologue overlaps the previous kernel's tail)",
                        "timing": f"median of {repeats} repeats of {args.steps} steps (CUDA events, max over ranks per repeat)",
+                       "kernels": (f"batch <= {f.NATIVE_AUTO_MAX}: six-bit codes straight into the tensor cores (weights also held in the 128x128 tile layout, activations as four exact e5m2 planes); larger batches: codes unpacked to fp16 patterns in tensor memory"
+                                   if ctx.get("native", True) and f.native_supported(e, m, 256, 64, 1) else "codes unpacked to fp16 patterns in tensor memory"),
                        "static_weights": bool(f.static_weights()),
                        "programmatic_gemm_launch": bool(f.lib().fp6b200_get_option(2) == 1)},
             "weight_gbs": bench_weight_gbs(layers, batches, e, m, sec_step),
@@ -660,6 +666,8 @@ def main():
                     help="also time torch's fp16 GEMM on GPU-dequantised weights for every case (single GPU)")
     ap.add_argument("--no-programmatic-launch", action="store_true",
                     help="plain stream order between a GEMM and the kernel before it")
+    ap.add_argument("--no-native", action="store_true",
+                    help="run every batch size on the fp16-pattern kernel (by default batches <= 32 of six-bit formats use the tensor cores' own FP6 inputs)")
     ap.add_argument("--no-static-weights", action="store_true",
                     help="do not let a GEMM read its (prepacked, read-only) weights before the previous kernel has completed")
     ap.add_argument("--case", default=None, help="LAYER:BATCH - run only this launch shape of the workload (for profiler captures)")

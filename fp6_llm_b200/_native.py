@@ -15,7 +15,7 @@ _ROOT = os.path.dirname(_PKG)
 _CSRC = os.path.join(_PKG, "csrc")
 LIB_DIR = os.path.join(_PKG, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libfp6_b200.so")
-SOURCES = ("fpx_gemm.cu", "fpx_prepack.cu", "c_api.cu", "c_api_noalloc.cu")
+SOURCES = ("fpx_gemm.cu", "fpx_native.cu", "fpx_prepack.cu", "c_api.cu", "c_api_noalloc.cu")
 HEADERS = ("fpx_internal.h", "fpx_layout.h", "ptx_sm100.cuh")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--threads", "4",
@@ -29,6 +29,8 @@ C_SYMBOLS = (
     "fp6b200_device_status", "fp6b200_linear_static_scratch", "fp6b200_static_scratch_bytes",
     "fp6b200_linear_gather", "fp6b200_set_option", "fp6b200_get_option", "fp6b200_quantize_prepack",
     "fp6b200_linear_host_io_batch", "fp6b200_kernel_launches", "fp6b200_linear_ex",
+    "fp6b200_native_supported", "fp6b200_native_weight_bytes", "fp6b200_native_workspace_bytes",
+    "fp6b200_native_repack", "fp6b200_linear_native", "fp6b200_native_kernel_launches", "fp6b200_linear_native_gather",
 )
 
 
@@ -92,6 +94,20 @@ def lib() -> ctypes.CDLL:
     L.fp6b200_linear.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, ci]
     L.fp6b200_linear_ex.restype = ci
     L.fp6b200_linear_ex.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, ci, vp, ci]
+    L.fp6b200_native_supported.restype = ci
+    L.fp6b200_native_supported.argtypes = [ci, ci, sz, sz, sz]
+    L.fp6b200_native_weight_bytes.restype = sz
+    L.fp6b200_native_weight_bytes.argtypes = [sz, sz]
+    L.fp6b200_native_workspace_bytes.restype = sz
+    L.fp6b200_native_workspace_bytes.argtypes = [sz, sz]
+    L.fp6b200_native_repack.restype = ci
+    L.fp6b200_native_repack.argtypes = [ci, ci, vp, vp, vp, sz, sz]
+    L.fp6b200_linear_native.restype = ci
+    L.fp6b200_linear_native.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, vp, ci]
+    L.fp6b200_linear_native_gather.restype = ci
+    L.fp6b200_linear_native_gather.argtypes = [ci, ci, vp, vp, vp, vp, vp, vp, vp, ci, ci, sz, sz, sz, sz, sz, vp]
+    L.fp6b200_native_kernel_launches.restype = ci
+    L.fp6b200_native_kernel_launches.argtypes = [sz, sz, sz]
     L.fp6b200_linear_host_io.restype = ci
     L.fp6b200_linear_host_io.argtypes = [ci, ci, vp, vp, vp, vp, sz, sz, sz, ci]
     L.fp6b200_linear_host_io_batch.restype = ci

@@ -149,6 +149,61 @@ int fp6b200_linear_ex(int e_bits, int m_bits, void* stream, const void* weight_p
                             static_cast<__half*>(out), M, N, K, workspace, split_k, status, nullptr, &epi);
 }
 
+int fp6b200_native_supported(int e_bits, int m_bits, size_t M, size_t N, size_t K) {
+    return fpx::native_format(e_bits, m_bits) && M > 0 && M % 256 == 0 && K > 0 && K % 64 == 0 && N > 0 &&
+           N <= (size_t)fpx::native_max_tokens();
+}
+
+size_t fp6b200_native_weight_bytes(size_t M, size_t K) { return fpx::native_weight_bytes(M, K); }
+
+size_t fp6b200_native_workspace_bytes(size_t N, size_t K) { return fpx::native_workspace_bytes(N, K); }
+
+int fp6b200_native_repack(int e_bits, int m_bits, void* stream, const void* weight_packed, void* weight_native, size_t M,
+                          size_t K) {
+    return fpx::launch_native_repack(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_packed, weight_native, M, K);
+}
+
+int fp6b200_linear_native(int e_bits, int m_bits, void* stream, const void* weight_native, const void* scales, const void* act,
+                          void* out, size_t M, size_t N, size_t K, void* workspace, const void* bias, int activation) {
+    int* status = status_ptr();
+    if (!status) return cudaErrorInitializationError;
+    fpx::Epilogue epi;
+    epi.bias = static_cast<const __half*>(bias);
+    epi.activation = activation;
+    return fpx::launch_native_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_native,
+                                   static_cast<const __half*>(scales), static_cast<const __half*>(act),
+                                   static_cast<__half*>(out), M, N, K, workspace, status, nullptr, &epi);
+}
+
+int fp6b200_linear_native_gather(int e_bits, int m_bits, void* stream, const void* weight_native_shard, const void* scales_shard,
+                                 const void* act, void* const* out_peers, void* const* flag_peers, void* epoch_counter,
+                                 int world, int rank, size_t out_rows, size_t row0, size_t M, size_t N, size_t K,
+                                 void* workspace) {
+    int* status = status_ptr();
+    if (!status) return cudaErrorInitializationError;
+    if (!out_peers || !flag_peers || world < 1 || world > fpx::kMaxOutTargets || rank < 0 || rank >= world)
+        return cudaErrorInvalidValue;
+    if (out_rows > 0x7fffffffull || row0 > 0x7fffffffull || row0 + M > out_rows || out_rows % 4 != 0 || row0 % 4 != 0)
+        return cudaErrorInvalidValue;
+    fpx::OutTargets targets = {};
+    uint32_t* flags[fpx::kMaxOutTargets] = {};
+    for (int r = 0; r < world; r++) {
+        targets.ptr[r] = static_cast<__half*>(out_peers[r]);
+        flags[r] = static_cast<uint32_t*>(flag_peers[r]);
+    }
+    targets.count = (uint32_t)world;
+    targets.ld = (uint32_t)out_rows;
+    targets.row0 = (uint32_t)row0;
+    cudaError_t err = fpx::launch_native_gemm(e_bits, m_bits, static_cast<cudaStream_t>(stream), weight_native_shard,
+                                              static_cast<const __half*>(scales_shard), static_cast<const __half*>(act),
+                                              nullptr, M, N, K, workspace, status, &targets);
+    if (err != cudaSuccess) return err;
+    return fpx::launch_gather_barrier(static_cast<cudaStream_t>(stream), flags, world, rank,
+                                      static_cast<uint32_t*>(epoch_counter), status);
+}
+
+int fp6b200_native_kernel_launches(size_t M, size_t N, size_t K) { return fpx::native_kernel_launches(M, N, K); }
+
 int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weight_shard, const void* scales_shard,
                           const void* act, void* const* out_peers, void* const* flag_peers, void* epoch_counter, int world,
                           int rank, size_t out_rows, size_t row0, size_t M, size_t N, size_t K, float* workspace,

@@ -63,11 +63,6 @@ constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kTmemCols = 512;      // the whole tensor memory: one CTA per SM
 
 
-// status codes written by a wait that gave up
-enum : int {
-    kErrStageEmpty = 1, kErrStageFull = 2, kErrAEmpty = 3, kErrAFull = 6, kErrAccFull = 7, kErrSmemAlign = 8,
-    kErrAccEmpty = 9, kErrPeerWait = 10   // 10: a peer GPU did not arrive at the end of a sharded layer
-};
 
 // Sleep between two polls of a barrier (ns).  Each failed poll costs issue slots the unpack warps need, so with the
 // long stages of the narrow tiles the copy producers (which run stages ahead of their consumers) and the issuing warps
@@ -803,6 +798,8 @@ cudaError_t make_act_map(CUtensorMap* map, const __half* act, size_t N, size_t K
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+}  // namespace
+
 // The work decomposition of one call (see WorkPlan): split_k == 0 is the library's own (data-parallel waves of tiles,
 // then the K blocks of the remaining tiles dealt out evenly), split_k >= 1 the caller's.  Returns the effective split.
 int make_plan(size_t M, size_t n_tiles, size_t K, int split_k, int sms, WorkPlan* out) {
@@ -843,6 +840,8 @@ int make_plan(size_t M, size_t n_tiles, size_t K, int split_k, int sms, WorkPlan
     plan_finalize(&plan);
     return eff_split;
 }
+
+namespace {
 
 template <int E_BITS, int M_BITS, int N_TILE>
 cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
@@ -949,6 +948,26 @@ static std::atomic<int> g_programmatic_launch{1};
 void set_programmatic_launch(int on) { g_programmatic_launch.store(on ? 1 : 0); }
 int programmatic_launch() { return g_programmatic_launch.load(); }
 
+// Sums the partial tiles a stream-K GEMM left in its slots (launched programmatically after it).
+cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, const float* workspace, size_t N,
+                                 int n_tile, const WorkPlan& plan, const Epilogue* epilogue) {
+    const uint32_t rem = plan_rem_tiles(plan);
+    if (rem == 0) return cudaSuccess;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rem, (unsigned)((n_tile + kFixupCols - 1) / kFixupCols));
+    cfg.blockDim = dim3(32u * kFixupCols);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int early = programmatic_launch() ? 1 : 0;
+    const __half* bias = epilogue ? epilogue->bias : nullptr;
+    const int activation = epilogue ? epilogue->activation : kActNone;
+    return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, workspace, (uint32_t)N, n_tile, plan, early, bias, activation);
+}
+
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
                         int* status, const OutTargets* targets, const Epilogue* epilogue) {
@@ -1016,17 +1035,7 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     if (plan.mode == kStreamK) {
         const uint32_t rem = plan_rem_tiles(plan);
         if (rem == 0) return cudaSuccess;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(rem, (unsigned)((n_tile + kFixupCols - 1) / kFixupCols));
-        cfg.blockDim = dim3(32u * kFixupCols);
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        const int early = programmatic_launch() ? 1 : 0;
-        return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, (const float*)workspace, (uint32_t)N, n_tile, plan, early, bias, activation);
+        return launch_streamk_fixup(stream, where, workspace, N, n_tile, plan, epilogue);
     }
     if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true, M, epilogue);
     return cudaSuccess;

@@ -23,6 +23,12 @@ inline bool format_supported(int e_bits, int m_bits) {
         else { constexpr int kE = 2, kM = 3; CALL; }                                  \
     } while (0)
 
+// Status codes a kernel's bounded wait records in the device status word when it gives up.
+enum : int {
+    kErrStageEmpty = 1, kErrStageFull = 2, kErrAEmpty = 3, kErrAFull = 6, kErrAccFull = 7, kErrSmemAlign = 8,
+    kErrAccEmpty = 9, kErrPeerWait = 10   // 10: a peer GPU did not arrive at the end of a sharded layer
+};
+
 // Where the fp16 result goes.  One target with ld == M and row0 == 0 is the plain layer.  Several targets are the
 // output buffers [N][ld] of the ranks of an OC-sharded layer (this GPU's and its peers', as mapped into this
 // process): the M rows computed here are stored at rows row0 .. row0 + M of every target.
@@ -50,6 +56,13 @@ struct Epilogue {
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
                         const __half* act, __half* out, size_t M, size_t N, size_t K, float* workspace, int split_k,
                         int* status, const OutTargets* targets = nullptr, const Epilogue* epilogue = nullptr);
+// Work decomposition of one call over `sms` CTAs (see WorkPlan): M rows in 128-row tiles, K in 64-wide blocks;
+// split_k == 0 is the library's own (waves of whole tiles, then the K blocks of the remaining tiles dealt out evenly),
+// split_k >= 1 the caller's.  Returns the effective split.
+struct WorkPlan;
+int make_plan(size_t M, size_t n_tiles, size_t K, int split_k, int sms, WorkPlan* out);
+cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, const float* workspace, size_t N,
+                                 int n_tile, const WorkPlan& plan, const Epilogue* epilogue);
 // Cross-GPU arrival barrier that ends a sharded layer: tells every peer that this rank's stores into its output
 // buffer are complete and waits (bounded) for the same word from every peer.  flag_peers[r] = rank r's flag array
 // (one 32-bit word per rank) as mapped here; epoch_counter = this rank's own call counter in device memory.
@@ -72,6 +85,20 @@ int gemm_kernel_launches(size_t M, size_t N, size_t K, int split_k);
 int device_sm_count();
 // Workspace the GEMM needs when it picks its own decomposition (split_k == 0).
 size_t gemm_auto_workspace_bytes(size_t N);
+
+// The tensor cores' own six-bit inputs (fpx_native.cu): e3m2 and e2m3 weights re-laid into 128 x 128 tiles that a tensor
+// copy expands in flight, activations split into four exact e5m2 planes; batches of up to native_max_tokens() tokens.
+bool native_format(int e_bits, int m_bits);
+int native_max_tokens();
+size_t native_weight_bytes(size_t M, size_t K);
+size_t native_workspace_bytes(size_t N, size_t K);
+cudaError_t launch_native_repack(int e_bits, int m_bits, cudaStream_t stream, const void* packed, void* native, size_t M,
+                                 size_t K);
+// workspace: native_workspace_bytes(N, K) bytes, 256-byte aligned (activation planes, then the stream-K slots)
+cudaError_t launch_native_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight_native, const __half* scales,
+                               const __half* act, __half* out, size_t M, size_t N, size_t K, void* workspace, int* status,
+                               const OutTargets* targets = nullptr, const Epilogue* epilogue = nullptr);
+int native_kernel_launches(size_t M, size_t N, size_t K);
 
 // Device address (current device) of the word in which a GEMM CTA records a time-out; nullptr on failure.
 int* gemm_status_word();

@@ -76,7 +76,7 @@ __device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, uint32_
 // Bounded wait.  Returns false when the CTA-wide abort word is (or becomes) non-zero: either another
 // thread gave up, or this wait itself ran past `timeout_ns`, in which case it records `code` there.
 // The clock and the abort word are only looked at between rounds of 1024 polls.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_word, int code, uint32_t sleep_ns,
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_word, int code, uint32_t sleep_ns,
                                             uint64_t timeout_ns) {
     const uint64_t t0 = global_timer_ns();
     for (;;) {
@@ -166,6 +166,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
         ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
         : "memory");
 }
+// 2-D tiled tensor copy global -> shared; x is the innermost coordinate.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar,
+                                            uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -206,6 +215,18 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// D[tmem] (+)= A[smem descriptor] * B[smem descriptor]; 8-, 6- or 4-bit floating-point inputs (each operand its own
+// format, given in the instruction descriptor), fp32 accumulate, K = 32 per instruction; one thread issues it.
+__device__ __forceinline__ void mma_f8f6f4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows of
 // 128 bytes (64 fp16), 8-row groups 1024 bytes apart, tile base 1024-byte aligned.
 __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
@@ -227,6 +248,13 @@ __device__ __host__ constexpr uint32_t idesc_f16_f32(uint32_t m, uint32_t n) {
            | (0u << 16)         // B K-major
            | ((n >> 3) << 17)   // N / 8
            | ((m >> 4) << 24);  // M / 16
+}
+
+// Instruction descriptor of kind::f8f6f4: operand formats 0 = e4m3, 1 = e5m2, 3 = e2m3, 4 = e3m2, 5 = e2m1; both
+// operands K-major, fp32 accumulator.
+constexpr uint32_t kFmtE4M3 = 0, kFmtE5M2 = 1, kFmtE2M3 = 3, kFmtE3M2 = 4, kFmtE2M1 = 5;
+__device__ __host__ constexpr uint32_t idesc_f8f6f4_f32(uint32_t a_format, uint32_t b_format, uint32_t m, uint32_t n) {
+    return (1u << 4) | (a_format << 7) | (b_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // One warp stores, for the 16 TMEM lanes starting at the lane of `taddr`, 32 consecutive 32-bit

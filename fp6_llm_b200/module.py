@@ -10,7 +10,23 @@ from __future__ import annotations
 import torch
 
 from .formats import bit_width, check_format, magnitudes
-from .ops import ACT_NONE, ACT_SILU_MUL, interleave_gate_up, linear_forward_ex, quantize_prepack_cuda
+from .ops import (ACT_NONE, ACT_SILU_MUL, NATIVE_AUTO_MAX, interleave_gate_up, linear_forward_ex, linear_forward_native,
+                  native_repack, native_supported, quantize_prepack_cuda)
+
+
+def _enable_native(layer) -> None:
+    rows = layer.weight.shape[0]
+    if not native_supported(layer.e_bits, layer.m_bits, rows, layer.in_features, 1):
+        raise ValueError("the tensor cores take six-bit codes only (e3m2, e2m3), with OC % 256 == 0 and IC % 64 == 0")
+    layer.register_buffer("weight_native", native_repack(layer.e_bits, layer.m_bits, layer.weight))
+
+
+def _forward(layer, flat: torch.Tensor, activation: int) -> torch.Tensor:
+    native = getattr(layer, "weight_native", None)
+    if native is not None and flat.shape[0] <= NATIVE_AUTO_MAX and layer.split_k == 0:
+        return linear_forward_native(layer.e_bits, layer.m_bits, flat, native, layer.scales, layer.bias, activation)
+    # the bias is added inside the kernel's fp32 epilogue, before the one rounding to fp16
+    return linear_forward_ex(layer.e_bits, layer.m_bits, flat, layer.weight, layer.scales, layer.split_k, layer.bias, activation)
 
 
 class FPxLinear(torch.nn.Module):
@@ -52,9 +68,14 @@ class FPxLinear(torch.nn.Module):
         if x.dtype != torch.float16 or x.shape[-1] != self.in_features:
             raise ValueError(f"expected fp16 activations [..., {self.in_features}]")
         flat = x.reshape(-1, self.in_features).contiguous()
-        # the bias is added inside the kernel's fp32 epilogue, before the one rounding to fp16
-        y = linear_forward_ex(self.e_bits, self.m_bits, flat, self.weight, self.scales, self.split_k, self.bias, ACT_NONE)
+        y = _forward(self, flat, ACT_NONE)
         return y.reshape(*x.shape[:-1], self.out_features)
+
+    def enable_native(self) -> "FPxLinear":
+        """Also keep the weights in the tile layout of the tensor cores' own six-bit inputs (e3m2 / e2m3 only; the weights
+        then occupy twice the memory): batches of up to NATIVE_AUTO_MAX tokens run on that path, larger ones as before."""
+        _enable_native(self)
+        return self
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, format=e{self.e_bits}m{self.m_bits}"
@@ -100,8 +121,13 @@ class FPxGateUpLinear(torch.nn.Module):
         if x.dtype != torch.float16 or x.shape[-1] != self.in_features:
             raise ValueError(f"expected fp16 activations [..., {self.in_features}]")
         flat = x.reshape(-1, self.in_features).contiguous()
-        y = linear_forward_ex(self.e_bits, self.m_bits, flat, self.weight, self.scales, self.split_k, self.bias, ACT_SILU_MUL)
+        y = _forward(self, flat, ACT_SILU_MUL)
         return y.reshape(*x.shape[:-1], self.out_features)
+
+    def enable_native(self) -> "FPxGateUpLinear":
+        """See :meth:`FPxLinear.enable_native`."""
+        _enable_native(self)
+        return self
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features} (gate and up fused), format=e{self.e_bits}m{self.m_bits}"

@@ -155,6 +155,73 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate, up], dim=1).reshape(gate.shape[0] * 2, *gate.shape[1:]).contiguous()
 
 
+# ----------------------------------------------------------------------------- the tensor cores' own six-bit inputs
+NATIVE_MAX_TOKENS = 64     # what linear_forward_native takes
+NATIVE_AUTO_MAX = 32       # up to this batch it measured faster than the fp16-pattern kernel on every LLaMA-2-70B layer
+
+
+def native_supported(EXPONENT: int, MANTISSA: int, OC: int, IC: int, B: int) -> bool:
+    """Whether :func:`linear_forward_native` takes this format and shape (e3m2 / e2m3, OC % 256 == 0, IC % 64 == 0,
+    1 <= B <= 64)."""
+    return bool(_native.lib().fp6b200_native_supported(EXPONENT, MANTISSA, OC, B, IC))
+
+
+def native_repack(EXPONENT: int, MANTISSA: int, _weights: torch.Tensor) -> torch.Tensor:
+    """Prepacked weights (int32 [OC, IC/32*6], the output of the packer) -> the tile layout :func:`linear_forward_native`
+    reads (uint8, 128 x 128 tiles of 12 KB, codes in little-endian bit order).  Once per weight tensor, on the GPU
+    (C: fp6b200_native_repack; the reference has no counterpart)."""
+    _require_cuda()
+    if not _weights.is_cuda or _weights.dtype != torch.int32 or not _weights.is_contiguous():
+        raise ValueError("expected a contiguous int32 CUDA tensor of prepacked weights")
+    OC, IC = _weights.shape[0], _in_channels(_weights, EXPONENT, MANTISSA)
+    L = _native.lib()
+    if not L.fp6b200_native_supported(EXPONENT, MANTISSA, OC, 1, IC):
+        raise ValueError("the native path takes e3m2 and e2m3 weights with OC % 256 == 0 and IC % 64 == 0")
+    dev = _weights.device
+    with torch.cuda.device(dev):
+        out = torch.empty(L.fp6b200_native_weight_bytes(OC, IC), dtype=torch.uint8, device=dev)
+        rc = L.fp6b200_native_repack(EXPONENT, MANTISSA, _stream_ptr(dev), _ptr(_weights), _ptr(out), OC, IC)
+    _native.check(rc, "fp6b200_native_repack")
+    return out
+
+
+def linear_forward_native(EXPONENT: int, MANTISSA: int, _in_feats: torch.Tensor, _weights_native: torch.Tensor,
+                          _scales: torch.Tensor, bias: torch.Tensor | None = None, activation: int = ACT_NONE) -> torch.Tensor:
+    """Out[B, OC] = In[B, IC] @ dequant(W)[OC, IC]^T with the weights in the layout of :func:`native_repack`, for up to
+    64 tokens (C: fp6b200_linear_native).  Same result as :func:`linear_forward_ex` up to fp32 summation order: the
+    activations enter the tensor cores as four exact e5m2 planes and the six-bit codes as they are."""
+    _require_cuda()
+    if _in_feats.dtype != torch.float16 or _scales.dtype != torch.float16 or _weights_native.dtype != torch.uint8:
+        raise ValueError("expected fp16 activations, uint8 native weights and fp16 scales")
+    if not (_in_feats.is_cuda and _weights_native.is_cuda and _scales.is_cuda):
+        raise ValueError("all tensors must be CUDA tensors")
+    if not (_in_feats.device == _weights_native.device == _scales.device):
+        raise ValueError("all tensors must be on the same device")
+    if _in_feats.dim() != 2 or not (_in_feats.is_contiguous() and _weights_native.is_contiguous() and _scales.is_contiguous()):
+        raise ValueError("activations must be a contiguous [B, IC]; weights and scales contiguous")
+    B, IC = _in_feats.shape
+    OC = _scales.numel()
+    L = _native.lib()
+    if not L.fp6b200_native_supported(EXPONENT, MANTISSA, OC, B, IC):
+        raise ValueError("the native path takes e3m2 / e2m3, OC % 256 == 0, IC % 64 == 0 and 1 <= B <= 64")
+    if _weights_native.numel() != L.fp6b200_native_weight_bytes(OC, IC):
+        raise ValueError("native weight tensor does not match OC (from the scales) and IC (from the activations)")
+    if activation not in (ACT_NONE, ACT_SILU_MUL):
+        raise ValueError("activation must be ACT_NONE or ACT_SILU_MUL")
+    if bias is not None and (bias.dtype != torch.float16 or bias.numel() != OC or bias.device != _in_feats.device
+                             or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous fp16 tensor with OC elements on the layer's device")
+    dev = _in_feats.device
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, L.fp6b200_native_workspace_bytes(B, IC))
+        out = torch.empty((B, OC // 2 if activation == ACT_SILU_MUL else OC), dtype=torch.float16, device=dev)
+        rc = L.fp6b200_linear_native(EXPONENT, MANTISSA, _stream_ptr(dev), _ptr(_weights_native), _ptr(_scales),
+                                     _ptr(_in_feats), _ptr(out), OC, B, IC, _ptr(ws),
+                                     _ptr(bias) if bias is not None else None, activation)
+    _native.check(rc, "fp6b200_linear_native")
+    return out
+
+
 def linear_forward_cuda(*args) -> torch.Tensor:
     """FP6 (e3m2) linear layer (fp6_linear_forward_cuda, fp6_llm/csrc/fp6_linear.cu:161-201).
 

@@ -179,12 +179,18 @@ class PeerExchange:
         out, _handle, out_ptrs = self._next_buffer(batch, oc)
         L = _native.lib()
         with torch.cuda.device(self.device):
-            nbytes = L.fp6b200_workspace_bytes(r1 - r0, batch, ic, split_k)
-            ws = _workspace(self.device, nbytes) if nbytes else None
-            rc = L.fp6b200_linear_gather(layer.e_bits, layer.m_bits, _stream_ptr(self.device), _ptr(layer.packed),
-                                         _ptr(layer.scale), _ptr(x), out_ptrs, self._flag_ptrs, _ptr(self.epoch),
-                                         self.world, self.rank, oc, r0, r1 - r0, batch, ic,
-                                         _ptr(ws) if ws is not None else None, split_k)
+            if layer.use_native(batch, split_k):
+                ws = _workspace(self.device, L.fp6b200_native_workspace_bytes(batch, ic))
+                rc = L.fp6b200_linear_native_gather(layer.e_bits, layer.m_bits, _stream_ptr(self.device), _ptr(layer.native),
+                                                    _ptr(layer.scale), _ptr(x), out_ptrs, self._flag_ptrs, _ptr(self.epoch),
+                                                    self.world, self.rank, oc, r0, r1 - r0, batch, ic, _ptr(ws))
+            else:
+                nbytes = L.fp6b200_workspace_bytes(r1 - r0, batch, ic, split_k)
+                ws = _workspace(self.device, nbytes) if nbytes else None
+                rc = L.fp6b200_linear_gather(layer.e_bits, layer.m_bits, _stream_ptr(self.device), _ptr(layer.packed),
+                                             _ptr(layer.scale), _ptr(x), out_ptrs, self._flag_ptrs, _ptr(self.epoch),
+                                             self.world, self.rank, oc, r0, r1 - r0, batch, ic,
+                                             _ptr(ws) if ws is not None else None, split_k)
         _native.check(rc, "fp6b200_linear_gather")
         return out
 
@@ -194,12 +200,27 @@ class ShardedFPxLinear:
     With `exchange` (a PeerExchange) the slabs are exchanged by the kernel itself, otherwise by one all-gather."""
 
     def __init__(self, packed_shard: torch.Tensor, scale_shard: torch.Tensor, plan: Sequence[Tuple[int, int]],
-                 rank: int, e_bits: int = 3, m_bits: int = 2, group=None, exchange: "PeerExchange | None" = None):
+                 rank: int, e_bits: int = 3, m_bits: int = 2, group=None, exchange: "PeerExchange | None" = None,
+                 native: bool = False):
         self.packed, self.scale, self.plan, self.rank = packed_shard, scale_shard, list(plan), rank
         self.e_bits, self.m_bits, self.group, self.exchange = e_bits, m_bits, group, exchange
+        # native=True: the shard is also kept in the tile layout of the tensor cores' own six-bit inputs, and batches of up
+        # to NATIVE_AUTO_MAX tokens run there (six-bit formats only; silently off for the others)
+        self.native = None
+        if native:
+            from .ops import native_repack, native_supported
+            ic = packed_shard.shape[1] * 32 // bit_width(e_bits, m_bits)
+            if native_supported(e_bits, m_bits, packed_shard.shape[0], ic, 1):
+                self.native = native_repack(e_bits, m_bits, packed_shard)
+
+    def use_native(self, batch: int, split_k: int) -> bool:
+        from .ops import NATIVE_AUTO_MAX
+        return self.native is not None and split_k == 0 and batch <= NATIVE_AUTO_MAX
 
     def forward_local(self, x: torch.Tensor, split_k: int = 0) -> torch.Tensor:
-        from .ops import linear_forward_eXmY_cuda
+        from .ops import linear_forward_eXmY_cuda, linear_forward_native
+        if self.use_native(x.shape[0], split_k):
+            return linear_forward_native(self.e_bits, self.m_bits, x, self.native, self.scale)
         return linear_forward_eXmY_cuda(self.e_bits, self.m_bits, x, self.packed, self.scale, split_k)
 
     def forward(self, x: torch.Tensor, split_k: int = 0) -> torch.Tensor:

@@ -57,6 +57,37 @@ int fp6b200_linear_ex(int e_bits, int m_bits, void* stream, const void* weight_p
                       void* out, size_t M, size_t N, size_t K, float* workspace, int split_k, const void* bias, int activation);
 
 /*
+ * The layer on the tensor cores' own six-bit inputs, for e3m2 and e2m3 weights and batches of up to 64 tokens (no
+ * counterpart in the reference, whose kernel - like fp6b200_linear - rebuilds an fp16 pattern of every weight with integer
+ * instructions before the MMA: fp6_llm/csrc/include/utils_parallel_dequant.cuh:24-63).  sm_100's tensor cores multiply
+ * e3m2 / e2m3 operands directly, and a tensor copy expands densely packed 6-bit codes on the way into shared memory, so
+ * no thread touches a weight and the layer streams its weights near the memory roofline.  The activations go in as four
+ * exact e5m2 planes (x = p0 + p1/4 + p2/32 + p3/256, written by a small kernel inside the call); every product is exact
+ * and accumulated in fp32, as in fp6b200_linear.
+ *   fp6b200_native_supported       1 if format (e3m2, e2m3) and shape (M % 256 == 0, K % 64 == 0, 1 <= N <= 64) are taken;
+ *   fp6b200_native_weight_bytes    bytes of the re-laid weights (tiles of 128 rows x 128 K, 12 KB each);
+ *   fp6b200_native_repack          once per weight tensor: prepacked weights (the output of fp6b200_prepack, i.e. of the
+ *                                  reference's weight_matrix_prepacking) -> the tile layout; device pointers, 16-byte aligned;
+ *   fp6b200_native_workspace_bytes scratch one call needs (activation planes + stream-K partials), 256-byte aligned;
+ *                                  calls that share a scratch buffer must be ordered on one stream;
+ *   fp6b200_linear_native          the layer; arguments as fp6b200_linear_ex, the library's own work decomposition.
+ */
+int fp6b200_native_supported(int e_bits, int m_bits, size_t M, size_t N, size_t K);
+size_t fp6b200_native_weight_bytes(size_t M, size_t K);
+size_t fp6b200_native_workspace_bytes(size_t N, size_t K);
+int fp6b200_native_repack(int e_bits, int m_bits, void* stream, const void* weight_packed, void* weight_native, size_t M,
+                          size_t K);
+int fp6b200_linear_native(int e_bits, int m_bits, void* stream, const void* weight_native, const void* scales, const void* act,
+                          void* out, size_t M, size_t N, size_t K, void* workspace, const void* bias, int activation);
+/* fp6b200_linear_gather (below) on the native path: the rank's shard in the tile layout, scratch as fp6b200_linear_native. */
+int fp6b200_linear_native_gather(int e_bits, int m_bits, void* stream, const void* weight_native_shard, const void* scales_shard,
+                                 const void* act, void* const* out_peers, void* const* flag_peers, void* epoch_counter,
+                                 int world, int rank, size_t out_rows, size_t row0, size_t M, size_t N, size_t K,
+                                 void* workspace);
+/* Kernels one fp6b200_linear_native call launches (0 for an unsupported shape). */
+int fp6b200_native_kernel_launches(size_t M, size_t N, size_t K);
+
+/*
  * Same layer with HOST activations and output: copies act to the device, runs the layer, copies the
  * result back and synchronises.  Weights and scales stay resident on the device (they are parameters).
  * Stands in for the torch-level call fp_eXmY_linear_forward_cuda (fp6_llm/csrc/fp6_linear.cu:269-313)
