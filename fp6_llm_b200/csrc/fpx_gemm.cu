@@ -653,19 +653,22 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(__half* __restrict__
     *reinterpret_cast<uint2*>(out + i) = packed;
 }
 
-// Fix-up of the stream-K remainder: CTA = (remainder tile, group of kFixupCols token columns); a thread owns four
-// consecutive output channels of one token column (32 threads per column).  Sums, in CTA order, the partial slots of every
-// CTA that worked on the tile (fp32, float4 loads) and stores fp16; tiles that one CTA computed alone were stored
-// directly and are skipped.
+// Fix-up of the stream-K remainder: CTA of 512 threads = (remainder tile, 16 / groups token columns) x groups; 32 threads
+// per column and group: a thread owns four consecutive output channels and every groups-th of the tile's partial slots
+// (fp32, float4 loads, all in flight at once: a tile of a large layer has ~40 parts, and summing them one thread after the
+// other cost ~6 us of load latency); the groups' sums are then added in group order, so the result does not depend on
+// timing.  The host picks groups (1..16) from the parts per tile, keeping the grid within about two CTAs per SM: the
+// CTAs are resident early and wait for the GEMM, and those that do not fit would run only after it.
+// Tiles that one CTA computed alone were stored directly and are skipped.
 // (Summing inside the GEMM by the CTA that delivers a tile's last part was measured slower: its dependent global
 // round trips cost more than this launch, and wide tiles are then summed by one SM instead of all.)
-constexpr int kFixupCols = 16;
+constexpr int kFixupThreads = 512;   // 16 (column, group) pairs of 32 threads
 constexpr uint64_t kEvenGridMinPercent = 85;
 constexpr uint64_t kFixupCostUnits = 20;   // the fix-up launch and its dependency cost about as much as 20 K blocks on one CTA
 constexpr uint64_t kMinUnitsPerCta = 8;   // a CTA is not started for fewer 64-K blocks than this (two 256-K stages)
-__global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
+__global__ void __launch_bounds__(kFixupThreads) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
                                                                          uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan,
-                                                                         int early_trigger, const __half* __restrict__ bias, int activation) {
+                                                                         int early_trigger, const __half* __restrict__ bias, int activation, uint32_t groups) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
@@ -699,14 +702,26 @@ __global__ void __launch_bounds__(32 * kFixupCols) streamk_fixup_kernel(const __
     const size_t slot_stride = (size_t)n_tile_size * kTileM;
     asm volatile("griddepcontrol.wait;" ::: "memory");       // the GEMM grid has completed and its stores are visible
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(11);
-    const uint32_t c = blockIdx.y * kFixupCols + (threadIdx.x >> 5);
+    __shared__ float4 group_sum[16][32];                      // [group * cols + column][lane]
+    const uint32_t cols = 16u / groups;
+    const uint32_t col = (threadIdx.x >> 5) % cols, grp = (threadIdx.x >> 5) / cols;
+    const uint32_t c = blockIdx.y * cols + col;
     const uint32_t n = n_tile * n_tile_size + c;
-    if (c < (uint32_t)n_tile_size && n < N) {
+    const bool live = c < (uint32_t)n_tile_size && n < N;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
         const float* base = slots + (size_t)c * kTileM + row4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (uint32_t i = 0; i < count; i++) {
+#pragma unroll 8
+        for (uint32_t i = grp; i < count; i += groups) {
             const float4 v = *reinterpret_cast<const float4*>(base + part_slot[i] * slot_stride);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    }
+    group_sum[threadIdx.x >> 5][threadIdx.x & 31u] = acc;
+    __syncthreads();
+    if (live && grp == 0) {
+        for (uint32_t g = 1; g < groups; g++) {
+            const float4 v = group_sum[g * cols + col][threadIdx.x & 31u];
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         const uint32_t m0 = m_tile * kTileM + row4;
@@ -953,9 +968,16 @@ cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, c
                                  int n_tile, const WorkPlan& plan, const Epilogue* epilogue) {
     const uint32_t rem = plan_rem_tiles(plan);
     if (rem == 0) return cudaSuccess;
+    // groups: as many as half the parts of a tile (about grid / rem CTAs share one), while the grid stays within ~2 CTAs per SM
+    const uint32_t parts = (plan.grid + rem - 1) / rem + 1;
+    uint32_t groups = 1;
+    while (groups < 16 && groups * 2 <= parts / 2 &&
+           (uint64_t)rem * ((n_tile + 16 / (groups * 2) - 1) / (16 / (groups * 2))) <= 2ull * (uint64_t)device_sm_count())
+        groups *= 2;
+    const uint32_t cols = 16 / groups;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rem, (unsigned)((n_tile + kFixupCols - 1) / kFixupCols));
-    cfg.blockDim = dim3(32u * kFixupCols);
+    cfg.gridDim = dim3(rem, (unsigned)((n_tile + cols - 1) / cols));
+    cfg.blockDim = dim3(kFixupThreads);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -965,7 +987,7 @@ cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, c
     const int early = programmatic_launch() ? 1 : 0;
     const __half* bias = epilogue ? epilogue->bias : nullptr;
     const int activation = epilogue ? epilogue->activation : kActNone;
-    return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, workspace, (uint32_t)N, n_tile, plan, early, bias, activation);
+    return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, workspace, (uint32_t)N, n_tile, plan, early, bias, activation, groups);
 }
 
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,

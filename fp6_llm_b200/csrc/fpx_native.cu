@@ -29,6 +29,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "fpx_internal.h"
 #include "fpx_layout.h"
@@ -57,11 +58,20 @@ struct NatCfg {
     static constexpr int tokens = N_TILE / kPieces;
     static constexpr uint32_t b_bytes = N_TILE * 128;
     static constexpr uint32_t stage_bytes = kNatTileSmem + b_bytes;
-    static constexpr int stages = (200 * 1024 / stage_bytes) < 8 ? (int)(200 * 1024 / stage_bytes) : 8;
+#ifndef NAT_RING_KB
+#define NAT_RING_KB 200
+#endif
+#ifndef NAT_NI_SMALL
+#define NAT_NI_SMALL 4
+#endif
     // issuer i takes the stages i, i + issuers, ... of the CTA's running count and owns two accumulators
-    static constexpr int issuers = N_TILE <= 64 ? 4 : (N_TILE <= 128 ? 2 : 1);
+    static constexpr int issuers = N_TILE <= 64 ? NAT_NI_SMALL : (N_TILE <= 128 ? 2 : 1);
+    static constexpr int ring_kb = N_TILE <= 64 ? NAT_RING_KB : 200;
+    static constexpr int fit = (int)(ring_kb * 1024 / stage_bytes) < 12 ? (int)(ring_kb * 1024 / stage_bytes) : 12;
+    static constexpr int stages = fit / issuers * issuers;
     static constexpr uint32_t acc_stride = 2 * N_TILE;                        // columns per issuer
-    static constexpr uint32_t tmem_cols = issuers * acc_stride < 32 ? 32 : issuers * acc_stride;
+    static constexpr uint32_t pow2_at_least(uint32_t x) { uint32_t p = 32; while (p < x) p *= 2; return p; }
+    static constexpr uint32_t tmem_cols = pow2_at_least(issuers * acc_stride);
     // an mbarrier wait sees only the parity of the phase: an issuer must meet a slot again on the slot's very next use
     static_assert(stages % issuers == 0, "ring depth must be a multiple of the issuers' stride");
     static_assert(tmem_cols <= 512 && (tmem_cols & (tmem_cols - 1)) == 0, "tensor memory");
@@ -88,7 +98,7 @@ struct NatParams {
 __device__ __forceinline__ float silu_mul_f(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
 
 template <int N_TILE>
-__global__ void __launch_bounds__(kNatThreads, 1)
+__global__ void __launch_bounds__(kNatThreads, N_TILE <= 64 ? 2 : 1)
 fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                   const __grid_constant__ NatParams p) {
     using Cfg = NatCfg<N_TILE>;
@@ -604,6 +614,10 @@ cudaError_t launch_native_gemm(int e_bits, int m_bits, cudaStream_t stream, cons
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     // 1. the activation planes
+#ifdef NAT_DEBUG_SKIP
+    static const int dbg_skip = getenv("FPX_NAT_SKIP") ? atoi(getenv("FPX_NAT_SKIP")) : 0;
+    if (!(dbg_skip & 1))
+#endif
     {
         const size_t threads = (size_t)tokens * (kpad / 8);
         cudaLaunchConfig_t cfg = {};
@@ -644,6 +658,9 @@ cudaError_t launch_native_gemm(int e_bits, int m_bits, cudaStream_t stream, cons
     }
     if (err != cudaSuccess) return err;
     // 3. the sum of the split tiles
+#ifdef NAT_DEBUG_SKIP
+    if (dbg_skip & 2) return cudaSuccess;
+#endif
     return launch_streamk_fixup(stream, where, slots, N, tokens, prm.plan, epilogue);
 }
 

@@ -71,6 +71,34 @@ def test_two_ranks_emulated_on_one_gpu(native_lib, oc, ic, bs):
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("oc,ic,bs", [(1024, 512, 3), (4096, 4096, 8), (2560, 1024, 30)])
+def test_two_ranks_emulated_on_one_gpu_native_path(native_lib, oc, ic, bs):
+    """The same exchange from the kernel that feeds the six-bit codes straight to the tensor cores."""
+    import fp6_llm_b200 as f
+    from fp6_llm_b200.sharding import plan_rows
+    L = native_lib
+    w, s = _layer(oc, ic, seed=oc + bs + 1)
+    x = torch.randn(bs, ic, generator=torch.Generator().manual_seed(7)).half().cuda()
+    plan = plan_rows(oc, 2)
+    outs = [torch.full((bs, oc), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+    epochs = [torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(2)]
+    ws = torch.empty(L.fp6b200_native_workspace_bytes(bs, ic), dtype=torch.uint8, device="cuda")
+    for rank, (r0, r1) in enumerate(plan):
+        native = f.native_repack(3, 2, f.weight_prepacking_cpu(w[r0:r1].contiguous()))
+        scale = s[r0:r1].contiguous()
+        flags[rank][1 - rank] = 1                                   # what the other rank's barrier would have written
+        rc = L.fp6b200_linear_native_gather(3, 2, None, native.data_ptr(), scale.data_ptr(), x.data_ptr(), _ptrs(outs), _ptrs(flags),
+                                            epochs[rank].data_ptr(), 2, rank, oc, r0, r1 - r0, bs, ic, ws.data_ptr())
+        assert rc == 0, L.fp6b200_error_string(rc)
+        assert f.device_status() == 0
+        expect = f.linear_forward_native(3, 2, x, native, scale)
+        for o in outs:
+            assert torch.equal(o[:, r0:r1], expect)
+        assert int(flags[1 - rank][rank].item()) == 1
+    assert torch.equal(outs[0], outs[1]) and not torch.isnan(outs[0]).any()
+
+
 def test_barrier_gives_up_when_a_peer_never_arrives(native_lib):
     """The wait for a peer is bounded: with a flag nobody sets the call still returns, the status word says so
     (code 10) and the device stays usable."""
