@@ -9,17 +9,21 @@
 //
 //   weights      re-laid once (native_repack_kernel) from the reference's packed format into tiles of 128 rows x 128 K,
 //                each 12 KB contiguous, codes in little-endian bit order; one tensor copy per tile and pipeline stage;
-//   activations  the tensor cores need an 8-bit (or narrower) partner, so split_activations_kernel writes every fp16
-//                activation as the EXACT sum of four e5m2 numbers, x = p0 + p1/4 + p2/32 + p3/256 (three significant bits
-//                each, truncated, the remainder carried on), as four byte planes [4 * tokens][K].  The planes are the
-//                columns of one MMA (N = 4 x tokens), so the four partial products land in four column groups of the
-//                accumulator and the epilogue adds them with their weights in fp32.  Every product e3m2 x e5m2 is exact
-//                and the sum is accumulated in fp32, as in the fp16 path;
-//   kernel       persistent, one CTA per SM: warp 0 copies weight tiles, warp 1 the activation planes, warps 2-5 issue
+//   activations  the tensor cores need an 8-bit (or narrower) partner, so every fp16 activation goes in as the EXACT sum of
+//                four e5m2 numbers, x = p0 + p1/4 + p2/32 + p3/256 (three significant bits each, truncated, the remainder
+//                carried on), i.e. as four byte planes.  The planes are the columns of one MMA (N = 4 x tokens), so the four
+//                partial products land in four column groups of the accumulator and the epilogue adds them with their
+//                weights in fp32.  Every product e3m2 x e5m2 is exact and the sum is accumulated in fp32, as in the fp16
+//                path.  Up to 4 tokens the planes are made inside the kernel: converter warps read the fp16
+//                activations of a stage [tokens x 128 K] from global memory (one visit ahead, into registers), split them
+//                with packed-half arithmetic and write the planes into the stage in the swizzled layout the MMA reads
+//                (no kernel before the GEMM); for 5..64 tokens split_activations_kernel writes the
+//                planes [4 * tokens][K] beforehand and a tensor copy brings them in;
+//   kernel       persistent, one CTA per SM: warp 0 copies weight tiles, warp 1 the activations, warps 2-5 issue
 //                the MMAs (four K = 32 steps per stage; one thread can issue an MMA only every ~110 cycles and a stage must
 //                not take more than ~550, so up to four warps take the stages in turn, each into its own accumulator),
 //                warps 6-9 are the epilogue (two accumulator buffers per issuer, so the epilogue of one segment runs
-//                under the main loop of the next).  Work plan, stream-K partials, fix-up kernel, output targets and
+//                under the main loop of the next), warps 10.. the converters.  Work plan, stream-K partials, fix-up kernel, output targets and
 //                fused epilogues are those of fpx_gemm.cu.
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records a code in the status word, frees its tensor memory
@@ -29,7 +33,6 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
 #include "fpx_internal.h"
 #include "fpx_layout.h"
@@ -48,8 +51,7 @@ constexpr int kPieces = 4;
 constexpr int kNatFirstIssuer = 2;             // warps 2..5: MMA issue (lane 0 of the first `issuers` of them)
 constexpr int kNatMaxIssuers = 4;
 constexpr int kNatFirstEpilogue = kNatFirstIssuer + kNatMaxIssuers;   // warps 6..9: one per tensor-memory lane quadrant
-constexpr int kNatWarps = kNatFirstEpilogue + 4;
-constexpr int kNatThreads = 32 * kNatWarps;
+constexpr int kNatFirstConverter = kNatFirstEpilogue + 4;   // warps 10..: split the fp16 activations (fused variant only)
 constexpr int kNatMaxTokens = 64;               // 4 x 64 = 256 MMA columns
 
 template <int N_TILE>
@@ -58,22 +60,29 @@ struct NatCfg {
     static constexpr int tokens = N_TILE / kPieces;
     static constexpr uint32_t b_bytes = N_TILE * 128;
     static constexpr uint32_t stage_bytes = kNatTileSmem + b_bytes;
-#ifndef NAT_RING_KB
-#define NAT_RING_KB 200
-#endif
-#ifndef NAT_NI_SMALL
-#define NAT_NI_SMALL 4
-#endif
-    // issuer i takes the stages i, i + issuers, ... of the CTA's running count and owns two accumulators
-    static constexpr int issuers = N_TILE <= 64 ? NAT_NI_SMALL : (N_TILE <= 128 ? 2 : 1);
-    static constexpr int ring_kb = N_TILE <= 64 ? NAT_RING_KB : 200;
-    static constexpr int fit = (int)(ring_kb * 1024 / stage_bytes) < 12 ? (int)(ring_kb * 1024 / stage_bytes) : 12;
+    // Up to 4 tokens the kernel splits the activations itself: conv_groups converter warps, warp g on the stages g,
+    // g + conv_groups, ... (a stage's conversion is a chain of dependent steps, so several stages must be in work at once;
+    // all warps on one stage measured 50 % slower than the separate kernel).  With more tokens the separate kernel
+    // measured faster (gate_up 57344 x 8192: 64.9 us against 65.7 us at 8 tokens, 66 us against 72 us at 16), whatever the
+    // number of converter warps.
+    static constexpr bool fused = N_TILE <= 16;
+    static constexpr int conv_groups = fused ? 4 : 0;
+    static constexpr int conv_width = 1;
+    static constexpr int conv_warps = conv_groups * conv_width;
+    static constexpr int warps = kNatFirstConverter + conv_warps;
+    static constexpr int threads = 32 * warps;
+    // issuer i takes the stages i, i + issuers, ... of the CTA's running count and owns two accumulators; three issuers and
+    // rings of 12 / 9 stages measured 1-4 % faster than four issuers and 8 stages (more weight bytes in flight)
+    static constexpr int issuers = N_TILE <= 16 ? 4 : (N_TILE <= 64 ? 3 : (N_TILE <= 128 ? 2 : 1));
+    static constexpr uint32_t ring_budget = 222 * 1024;
+    static constexpr int fit = (int)(ring_budget / stage_bytes) < 12 ? (int)(ring_budget / stage_bytes) : 12;
     static constexpr int stages = fit / issuers * issuers;
     static constexpr uint32_t acc_stride = 2 * N_TILE;                        // columns per issuer
     static constexpr uint32_t pow2_at_least(uint32_t x) { uint32_t p = 32; while (p < x) p *= 2; return p; }
     static constexpr uint32_t tmem_cols = pow2_at_least(issuers * acc_stride);
     // an mbarrier wait sees only the parity of the phase: an issuer must meet a slot again on the slot's very next use
     static_assert(stages % issuers == 0, "ring depth must be a multiple of the issuers' stride");
+    static_assert(!fused || stages % conv_groups == 0, "ring depth must be a multiple of the converter groups' stride");
     static_assert(tmem_cols <= 512 && (tmem_cols & (tmem_cols - 1)) == 0, "tensor memory");
     static constexpr uint32_t num_barriers = 2 * stages + 4;
     static constexpr uint32_t smem_bytes = stages * stage_bytes + 8 * num_barriers + 16;
@@ -88,7 +97,8 @@ struct NatParams {
     const __half* bias;
     uint32_t activation;
     float* workspace;           // stream-K partial slots [slot][tokens][128] fp32
-    uint32_t M, N;              // output channels, tokens
+    const __half* act;          // fp16 activations [N][K] (read by the converter warps of the fused variant)
+    uint32_t M, N, K;           // output channels, tokens, input channels
     uint32_t ktiles;            // ceil(K / 128)
     uint32_t a_format;          // operand format code of the weights (ptx::kFmtE3M2 / kFmtE2M3)
     WorkPlan plan;
@@ -98,7 +108,7 @@ struct NatParams {
 __device__ __forceinline__ float silu_mul_f(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
 
 template <int N_TILE>
-__global__ void __launch_bounds__(kNatThreads, N_TILE <= 64 ? 2 : 1)
+__global__ void __launch_bounds__(NatCfg<N_TILE>::threads, 1)
 fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                   const __grid_constant__ NatParams p) {
     using Cfg = NatCfg<N_TILE>;
@@ -107,7 +117,9 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     constexpr int NI = Cfg::issuers;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     const uint32_t ring = ptx::smem_u32(smem_dyn);
-    const uint32_t full = ring + S * Cfg::stage_bytes;   // per stage: weights and activation planes have landed
+    constexpr bool kFused = Cfg::fused;
+    constexpr int CW = Cfg::conv_warps;
+    const uint32_t full = ring + S * Cfg::stage_bytes;   // per stage: weights and activation planes are in place
     const uint32_t empty = full + 8 * S;                 // per stage: the MMAs that read it are done
     const uint32_t acc_full = empty + 8 * S;             // per accumulator buffer
     const uint32_t acc_empty = acc_full + 16;
@@ -126,7 +138,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     }
     if (warp == 0) {
         for (int i = lane; i < S; i += 32) {
-            ptx::mbar_init(full + 8 * i, 2);
+            ptx::mbar_init(full + 8 * i, kFused ? 1 + Cfg::conv_width : 2);   // the weight copy + the stage's converter warps (or the plane copy)
             ptx::mbar_init(empty + 8 * i, 1);
         }
         if (lane < 2) {
@@ -158,7 +170,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             ptx::RingPos<S> pos;
             pos.set(0);
             uint32_t issued = 0;
-            bool ok = true;
+            bool ok = !(kFused && acts);     // the fused variant has no activation copies: its converter warps read them
             SegmentIter iter;
             Segment seg;
             plan_start(plan, cta, &iter);
@@ -233,6 +245,112 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             }
         }
         __syncwarp();
+    } else if (warp >= kNatFirstConverter) {
+        // ------------------------------------------------------------ converters (fused variant): fp16 tile -> four e5m2 planes
+        // Every converter warp works on every stage: a thread takes chunks of 8 consecutive K of one token (16 bytes of the
+        // fp16 tile).  p0 = x with the mantissa cut to two bits (the upper byte of the pattern); the remainder x - p0 is
+        // exact in fp16, and so is 4 x it; the same step gives p1, p2 and p3 (scales 4, 8, 8), after which nothing is
+        // left: 11 significant bits fit into 3 + 3 + 3 + 3.  Bytes go to row piece * tokens + token of the stage's
+        // activation tile, 128 bytes per row with the 16-byte units of a row XOR-swizzled by the row (the 128-byte
+        // swizzle the MMA descriptor names).  Tokens past N arrive as zeros from the copy and give zero planes.
+        if constexpr (kFused) {
+            constexpr uint32_t CG = Cfg::conv_groups, WD = Cfg::conv_width;
+            const uint32_t grp = (uint32_t)(warp - kNatFirstConverter) / WD, sub = (uint32_t)(warp - kNatFirstConverter) % WD;
+            constexpr uint32_t kChunks = T * 16;                       // 16-byte chunks of a stage's activations
+            constexpr uint32_t kPerLane = (kChunks + WD * 32 - 1) / (WD * 32);
+            const __half2 four = __float2half2_rn(4.0f), eight = __float2half2_rn(8.0f);
+            const uint64_t keep = ptx::policy_evict_last();
+            // The group's stages in the CTA's running count are grp, grp + CG, ...  A cursor walks the plan to the K tile
+            // of each; the activations of the NEXT visit are requested before those of this visit are converted.
+            SegmentIter iter;
+            Segment seg;
+            plan_start(plan, cta, &iter);
+            bool have = plan_next(plan, cta, &iter, &seg);
+            uint32_t in_seg = grp;                                      // index of the cursor's stage inside its segment
+            auto settle = [&]() {                                       // move the cursor into the segment that holds its stage
+                while (have && in_seg >= seg.nkb) {
+                    in_seg -= seg.nkb;
+                    have = plan_next(plan, cta, &iter, &seg);
+                }
+            };
+            auto request = [&](uint4 (&dst)[kPerLane]) {                // loads of the cursor's stage
+                uint32_t kt = plan_first_stage(cta, seg.nkb) + in_seg;
+                if (kt >= seg.nkb) kt -= seg.nkb;
+                const uint32_t k0 = (seg.kb_begin + kt) * kNatTileK;
+#pragma unroll
+                for (uint32_t c = 0; c < kPerLane; c++) {
+                    const uint32_t chunk = (c * WD + sub) * 32 + lane;
+                    const uint32_t token = chunk >> 4, k = k0 + (chunk & 15u) * 8;
+                    dst[c] = make_uint4(0u, 0u, 0u, 0u);
+                    if (chunk < kChunks && token < p.N && k < p.K)      // K is a multiple of 8: a chunk is inside or outside
+                        asm volatile("ld.global.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"   // keep them in L2 under the weight stream
+                                     : "=r"(dst[c].x), "=r"(dst[c].y), "=r"(dst[c].z), "=r"(dst[c].w)
+                                     : "l"(p.act + (size_t)token * p.K + k), "l"(keep));
+                }
+            };
+            uint4 cur[kPerLane], nxt[kPerLane];
+            asm volatile("griddepcontrol.wait;" ::: "memory");          // the activations may come from the previous kernel
+            settle();
+            if (have) request(nxt);
+            uint32_t j = grp;                                           // running stage index of the visit
+            bool ok = true;
+            bool visit = have;                                          // the cursor's stage exists and its loads are in nxt
+            while (ok && visit) {
+#pragma unroll
+                for (uint32_t c = 0; c < kPerLane; c++) cur[c] = nxt[c];
+                in_seg += CG;
+                settle();
+                const bool more = have;
+                if (more) request(nxt);
+                // convert first (into registers), then wait for the stage: in the steady state every stage of the ring is in
+                // flight and a stage is handed back only every ~300 ns, so whatever follows that wait delays the stage
+                uint32_t plane[kPerLane][kPieces][2];
+#pragma unroll
+                for (uint32_t c = 0; c < kPerLane; c++) {
+                    const uint32_t h[4] = {cur[c].x, cur[c].y, cur[c].z, cur[c].w};
+                    uint32_t pc[kPieces][4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        uint32_t x = h[e];
+                        pc[0][e] = x;
+#pragma unroll
+                        for (int s = 1; s < kPieces; s++) {
+                            const uint32_t top = x & 0xff00ff00u;
+                            __half2 r = __hsub2(*reinterpret_cast<__half2*>(&x), *reinterpret_cast<const __half2*>(&top));
+                            r = __hmul2(r, s == 1 ? four : eight);
+                            x = *reinterpret_cast<uint32_t*>(&r);
+                            pc[s][e] = x;
+                        }
+                    }
+#pragma unroll
+                    for (int s = 0; s < kPieces; s++) {   // the upper bytes of the eight values, in K order
+                        plane[c][s][0] = __byte_perm(pc[s][0], pc[s][1], 0x7531);
+                        plane[c][s][1] = __byte_perm(pc[s][2], pc[s][3], 0x7531);
+                    }
+                }
+                ptx::RingPos<S> pos;
+                pos.set(j);
+                if (!ptx::mbar_wait_warp(empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, 40)) { ok = false; break; }
+                const uint32_t b_tile = ring + pos.idx * Cfg::stage_bytes + kNatTileSmem;
+#pragma unroll
+                for (uint32_t c = 0; c < kPerLane; c++) {
+                    const uint32_t chunk = (c * WD + sub) * 32 + lane;
+                    if (chunk >= kChunks) continue;
+                    const uint32_t token = chunk >> 4, k8 = chunk & 15u;       // K = 8 * k8 .. 8 * k8 + 7 of the stage
+#pragma unroll
+                    for (int s = 0; s < kPieces; s++) {
+                        const uint32_t row = (uint32_t)s * T + token;
+                        const uint32_t addr = b_tile + row * 128 + (((k8 >> 1) ^ (row & 7u)) << 4) + ((k8 & 1u) << 3);
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(plane[c][s][0]), "r"(plane[c][s][1]) : "memory");
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads shared memory through the async proxy
+                __syncwarp();
+                ptx::mbar_arrive_elected(full + 8 * pos.idx);
+                j += CG;
+                visit = more;
+            }
+        }
     } else {
         // ------------------------------------------------------------ epilogue: one warp per tensor-memory lane quadrant
         const int q = warp & 3;
@@ -504,7 +622,7 @@ cudaError_t launch_native_one(cudaStream_t stream, const CUtensorMap& w_map, con
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(prm.plan.grid);
-    cfg.blockDim = dim3(kNatThreads);
+    cfg.blockDim = dim3(NatCfg<N_TILE>::threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -589,6 +707,7 @@ cudaError_t launch_native_gemm(int e_bits, int m_bits, cudaStream_t stream, cons
 
     const int n_tile = native_n_tile(N);
     const int tokens = n_tile / kPieces;
+    const bool fused = n_tile <= 16;      // NatCfg<n_tile>::fused: the kernel splits the activations itself
     const size_t ktiles = native_ktiles(K);
     const size_t kpad = ktiles * kNatTileK;
     uint8_t* planes = static_cast<uint8_t*>(workspace);
@@ -606,19 +725,19 @@ cudaError_t launch_native_gemm(int e_bits, int m_bits, cudaStream_t stream, cons
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-        cuuint64_t xdims[2] = {(cuuint64_t)kpad, (cuuint64_t)n_tile};
-        cuuint64_t xstrides[1] = {(cuuint64_t)kpad};
-        cuuint32_t xbox[2] = {(cuuint32_t)kNatTileK, (cuuint32_t)n_tile};
-        r = enc(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, planes, xdims, xstrides, xbox, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (fused) {
+            x_map = w_map;   // not used: the converter warps read the activations themselves
+        } else {
+            cuuint64_t xdims[2] = {(cuuint64_t)kpad, (cuuint64_t)n_tile};
+            cuuint64_t xstrides[1] = {(cuuint64_t)kpad};
+            cuuint32_t xbox[2] = {(cuuint32_t)kNatTileK, (cuuint32_t)n_tile};
+            r = enc(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, planes, xdims, xstrides, xbox, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        }
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     // 1. the activation planes
-#ifdef NAT_DEBUG_SKIP
-    static const int dbg_skip = getenv("FPX_NAT_SKIP") ? atoi(getenv("FPX_NAT_SKIP")) : 0;
-    if (!(dbg_skip & 1))
-#endif
-    {
+    if (!fused) {
         const size_t threads = (size_t)tokens * (kpad / 8);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
@@ -642,8 +761,10 @@ cudaError_t launch_native_gemm(int e_bits, int m_bits, cudaStream_t stream, cons
     prm.bias = bias;
     prm.activation = (uint32_t)activation;
     prm.workspace = slots;
+    prm.act = act;
     prm.M = (uint32_t)M;
     prm.N = (uint32_t)N;
+    prm.K = (uint32_t)K;
     prm.ktiles = (uint32_t)ktiles;
     prm.a_format = e_bits == 3 ? ptx::kFmtE3M2 : ptx::kFmtE2M3;
     prm.status = status;
@@ -658,9 +779,6 @@ cudaError_t launch_native_gemm(int e_bits, int m_bits, cudaStream_t stream, cons
     }
     if (err != cudaSuccess) return err;
     // 3. the sum of the split tiles
-#ifdef NAT_DEBUG_SKIP
-    if (dbg_skip & 2) return cudaSuccess;
-#endif
     return launch_streamk_fixup(stream, where, slots, N, tokens, prm.plan, epilogue);
 }
 
@@ -669,7 +787,7 @@ int native_kernel_launches(size_t M, size_t N, size_t K) {
     const int sms = device_sm_count() < 256 ? device_sm_count() : 256;
     WorkPlan plan;
     make_plan(M, 1, native_ktiles(K) * kKBlock, 0, sms, &plan);
-    return 2 + (plan_rem_tiles(plan) ? 1 : 0);
+    return (native_n_tile(N) <= 16 ? 1 : 2) + (plan_rem_tiles(plan) ? 1 : 0);
 }
 
 }  // namespace fpx
