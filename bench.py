@@ -54,7 +54,11 @@ FALLBACK_TFLOPS = 1590.0
 MIN_TIMED_SECONDS = 0.25
 # DRAM bytes (read + write) per GEMM launch as a multiple of the launch's algorithmic bytes, from a profiler capture of
 # one layer of the workload (too large to capture whole); recorded when the capture was made, NOT measured in this run.
-RECORDED_TRAFFIC_RATIO = {}
+RECORDED_TRAFFIC_RATIO = {
+    "llama2-70b-fp6": (1.01, "profiler captures of single launches of this workload (gate_up at 1, 16 and 64 tokens: DRAM read + write "
+                             "= 1.012, 1.010 and 0.998 x the launch's algorithmic bytes; summaries under profiles/), scaled to the "
+                             "average launch of a step; recorded, not measured in this run"),
+}
 
 
 def alg_bytes(oc, ic, bs, bw, world=1):
@@ -530,7 +534,7 @@ def run_ours(args):
             for j, (mdl, bs) in enumerate(bench.cases):
                 key = (mdl["name"], bs)
                 layer = mdl["replicas"][(i * nb + j // nm) % bench.replicas]
-                calls.append((e, m, host_in[key], layer.packed, layer.scale, host_out[key], bench.split[key]))
+                calls.append((e, m, host_in[key], layer.packed, layer.scale, host_out[key], bench.split[key], layer.native))
             f.linear_forward_host_batch(calls)
         for i in range(3):
             e2e_step(i)

@@ -38,7 +38,8 @@ class HostCall(ctypes.Structure):
     """fp6b200_host_call of include/fp6_llm_b200.h."""
     _fields_ = [("e_bits", ctypes.c_int), ("m_bits", ctypes.c_int), ("weight_packed_dev", ctypes.c_void_p),
                 ("scales_dev", ctypes.c_void_p), ("act_host", ctypes.c_void_p), ("out_host", ctypes.c_void_p),
-                ("M", ctypes.c_size_t), ("N", ctypes.c_size_t), ("K", ctypes.c_size_t), ("split_k", ctypes.c_int)]
+                ("M", ctypes.c_size_t), ("N", ctypes.c_size_t), ("K", ctypes.c_size_t), ("split_k", ctypes.c_int),
+                ("weight_native_dev", ctypes.c_void_p)]
 
 
 def _nvcc() -> str:

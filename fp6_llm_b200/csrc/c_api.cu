@@ -294,6 +294,11 @@ cudaError_t batch_context(int n_calls, BatchContext** ctx) {
 }
 }  // namespace
 
+// whether a call of a host batch runs on the tensor cores' own six-bit inputs
+static bool host_call_native(const fp6b200_host_call& c) {
+    return c.weight_native_dev && c.split_k == 0 && c.N <= 32 && fp6b200_native_supported(c.e_bits, c.m_bits, c.M, c.N, c.K);
+}
+
 int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls) {
     if (!calls || n_calls <= 0) return cudaErrorInvalidValue;
     size_t total = 0, ws_bytes = 0;
@@ -301,7 +306,7 @@ int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls) {
         const fp6b200_host_call& c = calls[i];
         if (!c.act_host || !c.out_host || !c.weight_packed_dev || !c.scales_dev || c.split_k < 0) return cudaErrorInvalidValue;
         total += align_up(c.N * c.K * sizeof(__half), 256) + align_up(c.N * c.M * sizeof(__half), 256);
-        const size_t ws = fp6b200_workspace_bytes(c.M, c.N, c.K, c.split_k);
+        const size_t ws = host_call_native(c) ? fpx::native_workspace_bytes(c.N, c.K) : fp6b200_workspace_bytes(c.M, c.N, c.K, c.split_k);
         ws_bytes = ws > ws_bytes ? ws : ws_bytes;
     }
     std::lock_guard<std::mutex> lock(staging().mu);
@@ -325,8 +330,12 @@ int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls) {
         if ((err = cudaMemcpyAsync(act, c.act_host, act_bytes, cudaMemcpyHostToDevice, ctx->in)) != cudaSuccess) break;
         if ((err = cudaEventRecord(landed, ctx->in)) != cudaSuccess) break;
         if ((err = cudaStreamWaitEvent(ctx->compute, landed, 0)) != cudaSuccess) break;
-        err = fpx::launch_gemm(c.e_bits, c.m_bits, ctx->compute, c.weight_packed_dev, static_cast<const __half*>(c.scales_dev),
-                               act, out, c.M, c.N, c.K, ws, c.split_k, status);
+        if (host_call_native(c))
+            err = fpx::launch_native_gemm(c.e_bits, c.m_bits, ctx->compute, c.weight_native_dev, static_cast<const __half*>(c.scales_dev),
+                                          act, out, c.M, c.N, c.K, ws, status);
+        else
+            err = fpx::launch_gemm(c.e_bits, c.m_bits, ctx->compute, c.weight_packed_dev, static_cast<const __half*>(c.scales_dev),
+                                   act, out, c.M, c.N, c.K, ws, c.split_k, status);
         if (err != cudaSuccess) break;
         if ((err = cudaEventRecord(done, ctx->compute)) != cudaSuccess) break;
         if ((err = cudaStreamWaitEvent(ctx->out, done, 0)) != cudaSuccess) break;

@@ -1,4 +1,5 @@
-// FPx (e3m2 / e2m2) x fp16 linear layer for sm_100a:  Out[N, M] = Act[N, K] * dequant(W)[M, K]^T.
+// FPx x fp16 linear layer for sm_100a:  Out[N, M] = Act[N, K] * dequant(W)[M, K]^T, for every format the library takes
+// (e3m2, e2m2, e2m1, e3m1, e2m3) and any batch size, on weights in the reference's packed layout.
 //
 // Replaces the reference's QUANT_GEMM_Kernel + launcher
 // (fp6_llm/csrc/include/kernel_matmul.cuh:29-191, fp6_llm/csrc/fp6_linear.cu:11-102) with a persistent,
@@ -11,23 +12,30 @@
 //               map is needed and one copy per segment and row block covers the whole stage);
 //   warp 22     brings the stage's activation tile [N_TILE x 64 per K block] with one 3-D TMA tensor copy (128-byte
 //               swizzle, rows past N and K blocks past K zero-filled) onto a barrier of its own;
-//   warps 6-21  unpack the segments with shift/LOP3/PRMT sequences into fp16 bit patterns (code value / 2^bias,
-//               exact) and write them STRAIGHT INTO TENSOR MEMORY with tcgen05.st.16x128b: the
-//               reference's packed format hands every lane exactly the registers of an m16k16 A
-//               fragment, which is the register pattern of that store, so the dequantised weights
-//               never touch shared memory; the 16 warps work as teams on alternating stages;
+//   warps 6-21  unpack the segments into fp16 bit patterns (code value / 2^bias, exact) and write them STRAIGHT INTO
+//               TENSOR MEMORY with tcgen05.st.16x128b: the reference's packed format hands every lane exactly the
+//               registers of an m16k16 A fragment, which is the register pattern of that store, so the dequantised
+//               weights never touch shared memory.  The 16 warps are four groups of four (one warp per tensor-memory
+//               lane quadrant); the tensor-memory A operand is a ring of POSITIONS (one or two K blocks each), and
+//               group g takes the positions g, g + 4, ... of the CTA's running count: per visit it waits for the
+//               stage's weights, unpacks (for e3m2 / e2m2 with a sequence whose shifts are multiplications by
+//               kernel parameters, so that they issue on the FMA pipe beside the logic pipe: unpack16_mul), waits for
+//               the position's slot, stores, and hands the slot to the issuing warp;
 //   warps 0-3   issue tcgen05.mma.kind::f16 with A from tensor memory and B from shared memory, accumulating
-//               fp32 in tensor memory; narrow tiles are issued by up to four warps, each into its own
-//               accumulator, because one thread cannot issue MMAs fast enough for them.  At the end of a
-//               segment the same four warps (one per tensor-memory lane quadrant) read the accumulators
+//               fp32 in tensor memory; issuer i takes the positions i, i + issuers, ... (up to four issuers, each with
+//               its own accumulator, because one thread cannot issue MMAs fast enough for narrow tiles).  At the end
+//               of a segment the same four warps (one per tensor-memory lane quadrant) read the accumulators
 //               with tcgen05.ld, add them, multiply by 2^bias * scale[row] in fp32 (the per-row scale is
-//               applied here, once per output, not once per weight: the unpack warps are the bottleneck at
-//               small batch) and store fp16 output or fp32 partials.
+//               applied here, once per output, not once per weight), add the bias, apply the fused activation and
+//               store fp16 output - to this GPU's buffer or to every rank's - or fp32 partials.
+//
+// Six-bit weights and at most 64 tokens have a second path that does without the unpack warps altogether
+// (fpx_native.cu); this kernel is the general one.
 //
 // The kernel is launched programmatically: it starts while the previous kernel of the stream is finishing and every
 // role executes griddepcontrol.wait before it first touches global memory (weights that the caller declared
 // static are requested before that).  Ring depths are multiples of the stride of every role that visits only every
-// n-th stage (see Config).
+// n-th position (see Config).
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records a code in a status word, drains its
 // own copies, frees its tensor memory and returns.

@@ -361,17 +361,22 @@ def linear_forward_host(EXPONENT: int, MANTISSA: int, act_host: torch.Tensor, pa
 
 def linear_forward_host_batch(calls) -> None:
     """Several host-buffer layers as one pipelined batch (C: fp6b200_linear_host_io_batch): `calls` is a sequence of
-    (EXPONENT, MANTISSA, act_host, packed_dev, scales_dev, out_host, splitK); host tensors should be pinned.  The copy of
-    the next call's activations and of the previous call's result overlap the current call's kernels; returns when
-    every output has arrived."""
+    (EXPONENT, MANTISSA, act_host, packed_dev, scales_dev, out_host, splitK[, native_dev]); host tensors should be pinned.
+    The copy of the next call's activations and of the previous call's result overlap the current call's kernels; returns
+    when every output has arrived.  With native_dev (the weights in the layout of :func:`native_repack`) calls of up to
+    NATIVE_AUTO_MAX tokens with splitK == 0 run on the tensor cores' own six-bit inputs."""
     _require_cuda()
     calls = list(calls)
     if not calls:
         return
     arr = (_native.HostCall * len(calls))()
     dev = calls[0][3].device
-    for i, (e, m, act, packed, scales, out, split_k) in enumerate(calls):
+    for i, call in enumerate(calls):
+        e, m, act, packed, scales, out, split_k = call[:7]
+        native = call[7] if len(call) > 7 else None
         check_format(e, m)
+        if native is not None and (native.device != dev or native.dtype != torch.uint8 or not native.is_contiguous()):
+            raise ValueError("native weights must be a contiguous uint8 tensor on the batch's device")
         if packed.device != dev or scales.device != dev:
             raise ValueError("all layers of a batch must live on one device")
         if act.is_cuda or out.is_cuda or act.dtype != torch.float16 or out.dtype != torch.float16:
@@ -380,7 +385,8 @@ def linear_forward_host_batch(calls) -> None:
         OC = packed.shape[0]
         if _in_channels(packed, e, m) != IC or tuple(out.shape) != (B, OC) or not (act.is_contiguous() and out.is_contiguous()):
             raise ValueError("shape mismatch between activations, packed weights and output")
-        arr[i] = _native.HostCall(e, m, packed.data_ptr(), scales.data_ptr(), act.data_ptr(), out.data_ptr(), OC, B, IC, split_k)
+        arr[i] = _native.HostCall(e, m, packed.data_ptr(), scales.data_ptr(), act.data_ptr(), out.data_ptr(), OC, B, IC, split_k,
+                                  native.data_ptr() if native is not None else None)
     with torch.cuda.device(dev):
         rc = _native.lib().fp6b200_linear_host_io_batch(arr, len(calls))
     _native.check(rc, "fp6b200_linear_host_io_batch")

@@ -111,6 +111,9 @@ typedef struct fp6b200_host_call {
     void* out_host;         /* fp16 [N][M] */
     size_t M, N, K;
     int split_k;            /* as for fp6b200_linear; 0 = library decomposition */
+    const void* weight_native_dev;   /* NULL, or the same weights in the layout of fp6b200_native_repack: calls with
+                                        split_k == 0 and N <= 32 that fp6b200_native_supported accepts then run on
+                                        fp6b200_linear_native */
 } fp6b200_host_call;
 int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls);
 
@@ -186,8 +189,10 @@ int fp6b200_splitk_reduce(void* stream, void* out_dev, const float* partials_dev
  * every GPU that loads the library holds it until the process exits.  Returns cudaErrorInvalidValue (and says why on
  * stderr) when fp6b200_workspace_bytes(M, N, K, 0) exceeds that size (batch sizes above 64 on a 148-SM GPU).
  * Makes no cudaMalloc/cudaFree or other allocating call.  The first call on a device looks the array's address up
- * (cudaGetSymbolAddress).  All calls on a device share the array:
- * calls whose kernels can overlap on the GPU race; order them on one stream.
+ * (cudaGetSymbolAddress), and with lazy module loading (the CUDA default) that first touch is also when the driver
+ * places the library's device code and this array in device memory: a host that hands all free memory to its own pool
+ * must make one call (any supported shape) - or otherwise force the module to load - BEFORE it reserves the rest.
+ * All calls on a device share the array: calls whose kernels can overlap on the GPU race; order them on one stream.
  */
 int fp6b200_linear_static_scratch(int e_bits, int m_bits, void* stream, const void* weight_packed, const void* scales,
                                   const void* act, void* out, size_t M, size_t N, size_t K);

@@ -175,5 +175,14 @@ def test_batched_host_entry_matches_oracle(oracle_mod):
         f.linear_forward_host_batch(calls)
         for o, t in zip(outs, truths):
             _check(oracle_mod, o, t)
+    # the same batch with the six-bit layers also given in the tile layout: the two small-batch e3m2 calls take the
+    # tensor cores' own FP6 inputs, the others stay where they were
+    with_native = [c + ((f.native_repack(c[0], c[1], c[3]),) if (c[0], c[1]) == (3, 2) else (None,)) for c in calls]
+    for o in outs:
+        o.fill_(float("nan"))
+    f.linear_forward_host_batch(with_native)
+    assert f.device_status() == 0
+    for o, t in zip(outs, truths):
+        _check(oracle_mod, o, t)
     with pytest.raises(ValueError):
         f.linear_forward_host_batch([(3, 2, calls[0][2][:, :512].contiguous(), calls[0][3], calls[0][4], calls[0][5], 0)])
