@@ -163,18 +163,27 @@ def test_batched_host_entry_matches_oracle(oracle_mod):
     host outputs back, copies pipelined around the kernels."""
     import fp6_llm_b200 as f
     calls, truths, outs = [], [], []
-    for i, (e, m, oc, ic, bs) in enumerate(((3, 2, 1024, 1024, 24), (2, 2, 512, 2048, 3), (3, 2, 768, 4096, 130), (3, 2, 1024, 1024, 1))):
+    for i, (e, m, oc, ic, bs) in enumerate(((3, 2, 1024, 1024, 24), (2, 2, 512, 2048, 3), (3, 2, 768, 4096, 130), (3, 2, 1024, 1024, 1),
+                                             (3, 2, 16384, 1024, 130), (2, 2, 8192, 512, 300))):   # the last two: results of several MB
         packed, s, x, truth = _oracle_case(oracle_mod, e, m, oc, ic, bs, seed=40 + i)
         out = torch.empty(bs, oc, dtype=torch.float16).pin_memory()
         calls.append((e, m, x.cpu().pin_memory(), packed, s, out, 0))
         truths.append(truth)
         outs.append(out)
-    for _ in range(2):                                      # twice: the staging buffer and the events are reused
+    # four times with the same buffers (the staging buffer, streams and events are reused), with other activations in the
+    # same pinned buffers each time (scaled by a power of two, so the truth scales exactly)
+    base = [c[2].clone() for c in calls]
+    for factor in (1.0, 2.0, 0.5, 4.0):
+        for c, b in zip(calls, base):
+            c[2].copy_(b * factor)
         for o in outs:
             o.fill_(float("nan"))
         f.linear_forward_host_batch(calls)
+        assert f.device_status() == 0
         for o, t in zip(outs, truths):
-            _check(oracle_mod, o, t)
+            _check(oracle_mod, o, t * factor)
+    for c, b in zip(calls, base):
+        c[2].copy_(b)
     # the same batch with the six-bit layers also given in the tile layout: the two small-batch e3m2 calls take the
     # tensor cores' own FP6 inputs, the others stay where they were
     with_native = [c + ((f.native_repack(c[0], c[1], c[3]),) if (c[0], c[1]) == (3, 2) else (None,)) for c in calls]
