@@ -613,7 +613,7 @@ def run_ours(args):
                        "l2": f"inputs larger than L2: {replicas_main} replica(s) of the layer set ({shard_main * replicas_main / 2**20:.0f} MiB) rotated so a buffer is re-read only after >= 512 MiB of other weights",
                        "launch": "whole step replayed as a CUDA graph; kernels launched programmatically (prologue overlaps the previous kernel's tail)",
                        "timing": f"median of {repeats} repeats of {args.steps} steps (CUDA events, max over ranks per repeat)",
-                       "kernels": (f"batch <= {f.NATIVE_AUTO_MAX}: six-bit codes straight into the tensor cores (weights also held in the 128x128 tile layout, activations as four exact e5m2 planes); larger batches: codes unpacked to fp16 patterns in tensor memory"
+                       "kernels": (f"batch <= {f.NATIVE_AUTO_MAX}: codes straight into the tensor cores as e3m2 / e2m3 operands (weights also held in the 128x128 tile layout at 6 bits per weight, activations as four exact e5m2 planes); larger batches: codes unpacked to fp16 patterns in tensor memory"
                                    if ctx.get("native", True) and f.native_supported(e, m, 256, 64, 1) else "codes unpacked to fp16 patterns in tensor memory"),
                        "static_weights": bool(f.static_weights()),
                        "programmatic_gemm_launch": bool(f.lib().fp6b200_get_option(2) == 1)},
@@ -671,7 +671,7 @@ def main():
     ap.add_argument("--no-programmatic-launch", action="store_true",
                     help="plain stream order between a GEMM and the kernel before it")
     ap.add_argument("--no-native", action="store_true",
-                    help="run every batch size on the fp16-pattern kernel (by default batches <= 32 of six-bit formats use the tensor cores' own FP6 inputs)")
+                    help="run every batch size on the fp16-pattern kernel (by default batches <= 32 use the tensor cores' own FP6 inputs)")
     ap.add_argument("--no-static-weights", action="store_true",
                     help="do not let a GEMM read its (prepacked, read-only) weights before the previous kernel has completed")
     ap.add_argument("--case", default=None, help="LAYER:BATCH - run only this launch shape of the workload (for profiler captures)")

@@ -1,5 +1,7 @@
-// Six-bit weights on the tensor cores' own FP6 inputs (sm_100a): Out[N, M] = Act[N, K] * dequant(W)[M, K]^T for e3m2 and
-// e2m3 weights and batches of up to 64 tokens, the decode regime in which the layer is bound by streaming the weights.
+// Weights on the tensor cores' own FP6 inputs (sm_100a): Out[N, M] = Act[N, K] * dequant(W)[M, K]^T for batches of up to 64
+// tokens, the decode regime in which the layer is bound by streaming the weights.  e3m2 and e2m3 codes go in as they are;
+// the narrower formats (e2m2, e3m1, e2m1) are widened to the six-bit format with the same exponent field when the weights
+// are re-laid (their values are a subset of its values), so they stream 6 bits per weight here.
 //
 // The path of fpx_gemm.cu turns every weight into an fp16 pattern with integer instructions before the MMA
 // (as the reference does, fp6_llm/csrc/include/utils_parallel_dequant.cuh:24-63), and those instructions bound it
@@ -528,13 +530,13 @@ __global__ void __launch_bounds__(256) split_activations_kernel(const __half* __
 
 // ------------------------------------------------------------------------------------------------
 // Reference-packed weights -> native tiles.  A warp takes the 32 rows x 64 columns one unpack warp of the fp16 path
-// handles (same words, same unpack sequence), recovers the 6-bit codes from the fp16 patterns, gathers them in shared
-// memory and writes every 16 codes of a row as 12 bytes, code i at bits 6 i .. 6 i + 5.
+// handles (same words, same unpack sequence), recovers the codes from the fp16 patterns (widened to six bits), gathers
+// them in shared memory and writes every 16 codes of a row as 12 bytes, code i at bits 6 i .. 6 i + 5.
 template <int E_BITS, int M_BITS>
 __global__ void __launch_bounds__(128) native_repack_kernel(const uint8_t* __restrict__ packed, uint8_t* __restrict__ native,
                                                             uint32_t M, uint32_t K, uint32_t ktiles) {
     constexpr int BW = 1 + E_BITS + M_BITS;
-    static_assert(BW == 6, "six-bit formats only");
+    static_assert(BW <= 6, "codes of at most six bits");
     __shared__ uint8_t codes[4][32][64 + 4];
     const uint32_t kblocks = K / kKBlock;
     const int w = threadIdx.x >> 5;
@@ -545,14 +547,16 @@ __global__ void __launch_bounds__(128) native_repack_kernel(const uint8_t* __res
     const uint32_t kb = (unit >> 1) % kblocks, i = (unit >> 1) / kblocks;
     if (live) {
         const uint64_t tile = (uint64_t)i * kblocks + kb;
+        const uint32_t* r1 = reinterpret_cast<const uint32_t*>(packed + region_offset(BW, 1, M, K) + tile * tile_bytes(1));
         const uint32_t* r2 = reinterpret_cast<const uint32_t*>(packed + region_offset(BW, 2, M, K) + tile * tile_bytes(2));
         const uint32_t* r4 = reinterpret_cast<const uint32_t*>(packed + region_offset(BW, 4, M, K) + tile * tile_bytes(4));
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint32_t w4a = r4[(j * 4 + 2 * h + 0) * 32 + lane], w4b = r4[(j * 4 + 2 * h + 1) * 32 + lane];
-            const uint32_t w2 = r2[(j * 2 + h) * 32 + lane];
+            const uint32_t w2 = has_seg(BW, 2) ? r2[(j * 2 + h) * 32 + lane] : 0u;
+            const uint32_t w1 = has_seg(BW, 1) ? r1[j * 32 + lane] : 0u;
             uint32_t pat[8];
-            unpack16_any<E_BITS, M_BITS>(w4a, w4b, w2, 0u, h, pat);
+            unpack16_any<E_BITS, M_BITS>(w4a, w4b, w2, w1, h, pat);
 #pragma unroll
             for (int kk = 0; kk < 2; kk++)
 #pragma unroll
@@ -560,10 +564,13 @@ __global__ void __launch_bounds__(128) native_repack_kernel(const uint8_t* __res
                     const int row = 16 * kk + 8 * (a & 1) + g;
                     const int col = 16 * j + 8 * (a >> 1) + 2 * t;
                     const uint32_t v = pat[4 * kk + a];
-                    // pattern = sign | (exponent, mantissa) >> (5 - E): the code's low five bits sit below bit 15 - (5 - E)
-                    constexpr int sh = 10 - M_BITS;
-                    codes[w][row][col] = (uint8_t)(((v >> 10) & 0x20u) | ((v >> sh) & 0x1fu));
-                    codes[w][row][col + 1] = (uint8_t)(((v >> 26) & 0x20u) | ((v >> (16 + sh)) & 0x1fu));
+                    // pattern = sign | (exponent, mantissa) >> (5 - E): exponent and mantissa are the E + M bits from bit
+                    // 10 - M up.  The six-bit code of the same value in the hardware format with E exponent bits (e3m2
+                    // or e2m3) has the same fields with the mantissa extended by zeros: shift left by 5 - E - M.
+                    constexpr int sh = 10 - M_BITS, ext = 5 - E_BITS - M_BITS;
+                    constexpr uint32_t mask = (1u << (E_BITS + M_BITS)) - 1u;
+                    codes[w][row][col] = (uint8_t)(((v >> 10) & 0x20u) | (((v >> sh) & mask) << ext));
+                    codes[w][row][col + 1] = (uint8_t)(((v >> 26) & 0x20u) | (((v >> (16 + sh)) & mask) << ext));
                 }
         }
     }
@@ -635,7 +642,9 @@ cudaError_t launch_native_one(cudaStream_t stream, const CUtensorMap& w_map, con
 
 }  // namespace
 
-bool native_format(int e_bits, int m_bits) { return (e_bits == 3 && m_bits == 2) || (e_bits == 2 && m_bits == 3); }
+// Every format the library takes has its values among those of a six-bit tensor-core format with the same exponent width
+// and bias: e3m2 and e2m3 as they are, e3m1 inside e3m2, e2m2 and e2m1 inside e2m3 (mantissa extended by zero bits).
+bool native_format(int e_bits, int m_bits) { return format_supported(e_bits, m_bits); }
 int native_max_tokens() { return kNatMaxTokens; }
 int native_n_tile(size_t N) { return N <= 4 ? 16 : (N <= 8 ? 32 : (N <= 16 ? 64 : (N <= 32 ? 128 : 256))); }
 static size_t native_ktiles(size_t K) { return (K + kNatTileK - 1) / kNatTileK; }
@@ -666,8 +675,7 @@ cudaError_t launch_native_repack(int e_bits, int m_bits, cudaStream_t stream, co
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
     const uint8_t* in = static_cast<const uint8_t*>(packed);
     uint8_t* out = static_cast<uint8_t*>(native);
-    if (e_bits == 3) native_repack_kernel<3, 2><<<(unsigned)blocks, 128, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K, (uint32_t)ktiles);
-    else native_repack_kernel<2, 3><<<(unsigned)blocks, 128, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K, (uint32_t)ktiles);
+    FPX_DISPATCH_FORMAT(e_bits, m_bits, (native_repack_kernel<kE, kM><<<(unsigned)blocks, 128, 0, stream>>>(in, out, (uint32_t)M, (uint32_t)K, (uint32_t)ktiles)));
     return cudaGetLastError();
 }
 

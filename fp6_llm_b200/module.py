@@ -17,7 +17,7 @@ from .ops import (ACT_NONE, ACT_SILU_MUL, NATIVE_AUTO_MAX, interleave_gate_up, l
 def _enable_native(layer) -> None:
     rows = layer.weight.shape[0]
     if not native_supported(layer.e_bits, layer.m_bits, rows, layer.in_features, 1):
-        raise ValueError("the tensor cores take six-bit codes only (e3m2, e2m3), with OC % 256 == 0 and IC % 64 == 0")
+        raise ValueError("the tile layout needs OC % 256 == 0 and IC % 64 == 0")
     layer.register_buffer("weight_native", native_repack(layer.e_bits, layer.m_bits, layer.weight))
 
 
@@ -72,8 +72,8 @@ class FPxLinear(torch.nn.Module):
         return y.reshape(*x.shape[:-1], self.out_features)
 
     def enable_native(self) -> "FPxLinear":
-        """Also keep the weights in the tile layout of the tensor cores' own six-bit inputs (e3m2 / e2m3 only; the weights
-        then occupy twice the memory): batches of up to NATIVE_AUTO_MAX tokens run on that path, larger ones as before."""
+        """Also keep the weights in the tile layout of the tensor cores' own six-bit inputs (6 more bits per weight,
+        whatever the format): batches of up to NATIVE_AUTO_MAX tokens run on that path, larger ones as before."""
         _enable_native(self)
         return self
 

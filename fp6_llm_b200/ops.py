@@ -161,22 +161,22 @@ NATIVE_AUTO_MAX = 32       # up to this batch it measured faster than the fp16-p
 
 
 def native_supported(EXPONENT: int, MANTISSA: int, OC: int, IC: int, B: int) -> bool:
-    """Whether :func:`linear_forward_native` takes this format and shape (e3m2 / e2m3, OC % 256 == 0, IC % 64 == 0,
-    1 <= B <= 64)."""
+    """Whether :func:`linear_forward_native` takes this format and shape (OC % 256 == 0, IC % 64 == 0, 1 <= B <= 64)."""
     return bool(_native.lib().fp6b200_native_supported(EXPONENT, MANTISSA, OC, B, IC))
 
 
 def native_repack(EXPONENT: int, MANTISSA: int, _weights: torch.Tensor) -> torch.Tensor:
-    """Prepacked weights (int32 [OC, IC/32*6], the output of the packer) -> the tile layout :func:`linear_forward_native`
-    reads (uint8, 128 x 128 tiles of 12 KB, codes in little-endian bit order).  Once per weight tensor, on the GPU
-    (C: fp6b200_native_repack; the reference has no counterpart)."""
+    """Prepacked weights (int32 [OC, IC/32*bw], the output of the packer) -> the tile layout :func:`linear_forward_native`
+    reads (uint8, 128 x 128 tiles of 12 KB, six-bit codes in little-endian bit order; codes narrower than six bits are
+    widened to the tensor-core format with the same exponent field, which holds their values exactly).  Once per weight
+    tensor, on the GPU (C: fp6b200_native_repack; the reference has no counterpart)."""
     _require_cuda()
     if not _weights.is_cuda or _weights.dtype != torch.int32 or not _weights.is_contiguous():
         raise ValueError("expected a contiguous int32 CUDA tensor of prepacked weights")
     OC, IC = _weights.shape[0], _in_channels(_weights, EXPONENT, MANTISSA)
     L = _native.lib()
     if not L.fp6b200_native_supported(EXPONENT, MANTISSA, OC, 1, IC):
-        raise ValueError("the native path takes e3m2 and e2m3 weights with OC % 256 == 0 and IC % 64 == 0")
+        raise ValueError("the native path needs OC % 256 == 0 and IC % 64 == 0")
     dev = _weights.device
     with torch.cuda.device(dev):
         out = torch.empty(L.fp6b200_native_weight_bytes(OC, IC), dtype=torch.uint8, device=dev)
@@ -203,7 +203,7 @@ def linear_forward_native(EXPONENT: int, MANTISSA: int, _in_feats: torch.Tensor,
     OC = _scales.numel()
     L = _native.lib()
     if not L.fp6b200_native_supported(EXPONENT, MANTISSA, OC, B, IC):
-        raise ValueError("the native path takes e3m2 / e2m3, OC % 256 == 0, IC % 64 == 0 and 1 <= B <= 64")
+        raise ValueError("the native path takes OC % 256 == 0, IC % 64 == 0 and 1 <= B <= 64")
     if _weights_native.numel() != L.fp6b200_native_weight_bytes(OC, IC):
         raise ValueError("native weight tensor does not match OC (from the scales) and IC (from the activations)")
     if activation not in (ACT_NONE, ACT_SILU_MUL):

@@ -205,7 +205,7 @@ class ShardedFPxLinear:
         self.packed, self.scale, self.plan, self.rank = packed_shard, scale_shard, list(plan), rank
         self.e_bits, self.m_bits, self.group, self.exchange = e_bits, m_bits, group, exchange
         # native=True: the shard is also kept in the tile layout of the tensor cores' own six-bit inputs, and batches of up
-        # to NATIVE_AUTO_MAX tokens run there (six-bit formats only; silently off for the others)
+        # to NATIVE_AUTO_MAX tokens run there
         self.native = None
         if native:
             from .ops import native_repack, native_supported

@@ -57,14 +57,16 @@ int fp6b200_linear_ex(int e_bits, int m_bits, void* stream, const void* weight_p
                       void* out, size_t M, size_t N, size_t K, float* workspace, int split_k, const void* bias, int activation);
 
 /*
- * The layer on the tensor cores' own six-bit inputs, for e3m2 and e2m3 weights and batches of up to 64 tokens (no
+ * The layer on the tensor cores' own six-bit inputs, for batches of up to 64 tokens (no
  * counterpart in the reference, whose kernel - like fp6b200_linear - rebuilds an fp16 pattern of every weight with integer
  * instructions before the MMA: fp6_llm/csrc/include/utils_parallel_dequant.cuh:24-63).  sm_100's tensor cores multiply
  * e3m2 / e2m3 operands directly, and a tensor copy expands densely packed 6-bit codes on the way into shared memory, so
  * no thread touches a weight and the layer streams its weights near the memory roofline.  The activations go in as four
  * exact e5m2 planes (x = p0 + p1/4 + p2/32 + p3/256, written by a small kernel inside the call); every product is exact
  * and accumulated in fp32, as in fp6b200_linear.
- *   fp6b200_native_supported       1 if format (e3m2, e2m3) and shape (M % 256 == 0, K % 64 == 0, 1 <= N <= 64) are taken;
+ * Formats: e3m2 and e2m3 as they are; e2m2, e3m1 and e2m1 are widened to the six-bit format with the same exponent
+ * field when the weights are re-laid (exact: their values are a subset), so every format occupies 6 bits per weight here.
+ *   fp6b200_native_supported       1 if format and shape (M % 256 == 0, K % 64 == 0, 1 <= N <= 64) are taken;
  *   fp6b200_native_weight_bytes    bytes of the re-laid weights (tiles of 128 rows x 128 K, 12 KB each);
  *   fp6b200_native_repack          once per weight tensor: prepacked weights (the output of fp6b200_prepack, i.e. of the
  *                                  reference's weight_matrix_prepacking) -> the tile layout; device pointers, 16-byte aligned;

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 REL_FRO = 2e-3
 ROW_MAX = 1e-2
-NATIVE_FORMATS = ((3, 2), (2, 3))
+NATIVE_FORMATS = ((3, 2), (2, 3), (2, 2), (3, 1), (2, 1))   # the last three are widened to e2m3 / e3m2 / e2m3 codes
 
 
 def _native_from_codes(codes: np.ndarray) -> np.ndarray:
@@ -49,7 +49,10 @@ def test_repack_matches_numpy(e, m, oc, ic):
     packed = f.weight_prepacking_eXmY_cpu(e, m, w.cuda())
     native = f.native_repack(e, m, packed)
     assert native.dtype == torch.uint8 and native.numel() == (oc // 128) * ((ic + 127) // 128) * 128 * 96
-    expect = _native_from_codes(unpack_codes(w, e, m).numpy())
+    codes = unpack_codes(w, e, m).numpy().astype(np.uint32)
+    bw = 1 + e + m
+    six = ((codes >> (bw - 1)) << 5) | ((codes & ((1 << (bw - 1)) - 1)) << (6 - bw))      # sign kept, mantissa extended by zeros
+    expect = _native_from_codes(six.astype(np.uint8))
     assert np.array_equal(native.cpu().numpy(), expect)
 
 
@@ -141,7 +144,7 @@ def test_native_epilogues(oracle_mod, oc, ic, bs):
 def test_native_rejects_what_it_does_not_take():
     import fp6_llm_b200 as f
     from fp6_llm_b200.formats import random_codes_layer
-    assert not f.native_supported(2, 2, 512, 1024, 8)            # five-bit codes are not a tensor-core input
+    assert not f.native_supported(3, 3, 512, 1024, 8)            # not a format of the library
     assert not f.native_supported(3, 2, 512, 1024, 65)
     assert not f.native_supported(3, 2, 384, 1024, 8)
     w, s = random_codes_layer(512, 1024, 3, 2, seed=1)
@@ -150,9 +153,9 @@ def test_native_rejects_what_it_does_not_take():
         f.linear_forward_native(3, 2, torch.zeros(65, 1024, dtype=torch.float16, device="cuda"), native, s.cuda())
     with pytest.raises(ValueError):
         f.linear_forward_native(3, 2, torch.zeros(8, 2048, dtype=torch.float16, device="cuda"), native, s.cuda())
-    w5, _ = random_codes_layer(512, 1024, 2, 2, seed=1)
+    w5, _ = random_codes_layer(384, 1024, 2, 2, seed=1)
     with pytest.raises(ValueError):
-        f.native_repack(2, 2, f.weight_prepacking_eXmY_cpu(2, 2, w5.cuda()))
+        f.native_repack(2, 2, f.weight_prepacking_eXmY_cpu(2, 2, w5.cuda()))      # OC % 256 != 0
 
 
 def test_native_repeated_calls_on_one_stream_share_the_scratch(oracle_mod):
