@@ -384,7 +384,7 @@ class Bench:
             us = float(t.item())
         return us
 
-    def per_case(self, compare_cublas=False, split_sweep=None):
+    def per_case(self, compare_cublas=False, split_sweep=None, compare_reference=False):
         torch, f, ctx = self.torch, self.f, self.ctx
         hbm_peak, tc_peak, _ = ctx["peaks"]
         world = ctx["world"]
@@ -412,6 +412,31 @@ class Bench:
                 entry["split_k_sweep_us"] = sweep
                 entry["choose_split_k"] = chosen
                 entry["reference_heuristic_split_k"] = f.HeuristicFuntion_SplitK(mdl["oc"], bs, ctx["sms"])
+            if compare_reference and world == 1 and (self.e, self.m) in ((3, 2), (2, 2)):
+                # the reference's own kernel (sm_80 code: mma.sync, ldmatrix, cp.async) recompiled for sm_100a, on the same
+                # packed weights, with the split-K its heuristic picks; cold L2 like everything else
+                import oracle
+                R = oracle.ref_gpu()
+                sk = f.HeuristicFuntion_SplitK(mdl["oc"], bs, ctx["sms"])
+                ws_ref = torch.empty(max(sk, 1) * mdl["oc"] * bs, dtype=torch.float32, device=ctx["dev"])
+                out_ref = torch.empty(bs, mdl["oc"], dtype=torch.float16, device=ctx["dev"])
+
+                def ref_call(r):
+                    rc = R.ref_gpu_linear(self.e, self.m, torch.cuda.current_stream().cuda_stream, mdl["replicas"][r].packed.data_ptr(),
+                                          mdl["scale"].data_ptr(), x.data_ptr(), out_ref.data_ptr(), mdl["oc"], bs, mdl["ic"],
+                                          ws_ref.data_ptr(), sk)
+                    assert rc == 0, f"reference kernel returned {rc}"
+                with torch.cuda.stream(ctx["stream"]):
+                    ref_call(0)
+                torch.cuda.synchronize(ctx["dev"])
+                mine = mdl["replicas"][0].forward(x, self.split[key]).float()
+                rel = float((out_ref.float() - mine).norm() / mine.norm())
+                us_ref = self.time_graph(ref_call, n_rep)
+                entry["reference_kernel_us"] = round(us_ref, 3)
+                entry["reference_kernel_split_k"] = sk
+                entry["speedup_vs_reference_kernel"] = round(us_ref / us, 3)
+                entry["reference_kernel_rel_diff"] = round(rel, 6)
+                del ws_ref, out_ref
             if compare_cublas and world == 1:
                 # the same layer as a library fp16 GEMM on weights dequantised on the GPU (2.67x / 3.2x the bytes), cold L2
                 w16 = f.dequant_packed_cuda(self.e, self.m, mdl["packed"], mdl["scale"])
@@ -520,7 +545,10 @@ def run_ours(args):
             bench.graphs = []
 
     # ---- per-case device times (separate pass, each case alone in a graph over its replicas)
-    per_case = bench.per_case(compare_cublas=args.compare_cublas) if (world == 1 or args.per_case_multi) else []
+    import oracle as _oracle
+    ref_kernel = world == 1 and not args.no_reference_kernel and _oracle.have_ref_gpu()
+    per_case = (bench.per_case(compare_cublas=args.compare_cublas, compare_reference=ref_kernel)
+                if (world == 1 or args.per_case_multi) else [])
 
     # ---- end to end through the batched host-buffer entry point (single GPU only: it is a per-GPU call)
     e2e = None
@@ -586,7 +614,8 @@ def run_ours(args):
             entry["batch_sizes"] = batches2
             entry["repeats"] = rep2
             entry["cases"] = b2.per_case(compare_cublas=name.endswith("prefill-fp6"),
-                                         split_sweep=(1, 2, 4, 8) if name == "llama2-13b-fp5" else None)
+                                         split_sweep=(1, 2, 4, 8) if name == "llama2-13b-fp5" else None,
+                                         compare_reference=ref_kernel)
             if name.endswith("prefill-fp6"):
                 entry["tensor_peak_tflops"] = tc_peak
                 entry["frac_of_tensor_peak"] = entry["value"] / tc_peak
@@ -627,6 +656,15 @@ def run_ours(args):
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_step * args.steps * repeats, "clocks": clocks,
             "device_status": status, "cases": per_case,
         }
+        timed_ref = [c for c in per_case if "reference_kernel_us" in c]
+        if timed_ref and len(timed_ref) == len(per_case):
+            ref_us, own_us = sum(c["reference_kernel_us"] for c in timed_ref), sum(c["us"] for c in timed_ref)
+            line["reference_kernel"] = {
+                "us_per_step": round(ref_us, 1), "ours_us_per_step": round(own_us, 1), "speedup": round(ref_us / own_us, 3),
+                "what": "the reference's own GPU kernel (fp6_llm/csrc/fp6_linear.cu: sm_80 code - mma.sync, ldmatrix, cp.async - recompiled "
+                        "for sm_100a into oracle/_ref) on the same prepacked weights and activations, split-K from its heuristic for "
+                        f"{ctx['sms']} SMs, every case alone in a graph with cold L2; sums over the cases of a step",
+                "max_rel_diff_to_ours": max(c["reference_kernel_rel_diff"] for c in timed_ref)}
         if multi is not None:
             line["multi_gpu_check"] = multi
         if others is not None:
@@ -670,6 +708,8 @@ def main():
                     help="also time torch's fp16 GEMM on GPU-dequantised weights for every case (single GPU)")
     ap.add_argument("--no-programmatic-launch", action="store_true",
                     help="plain stream order between a GEMM and the kernel before it")
+    ap.add_argument("--no-reference-kernel", action="store_true",
+                    help="single GPU: do not also time the reference's own GPU kernel (recompiled for sm_100a, oracle/_ref) per case")
     ap.add_argument("--no-native", action="store_true",
                     help="run every batch size on the fp16-pattern kernel (by default batches <= 32 use the tensor cores' own FP6 inputs)")
     ap.add_argument("--no-static-weights", action="store_true",

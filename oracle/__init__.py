@@ -23,6 +23,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ORACLE_SO = os.path.join(_HERE, "_build", "liboracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libfp6_ref.so")
+_REF_GPU_SO = os.path.join(_HERE, "_ref", "libfp6_ref_gpu.so")
 
 
 def _find_reference() -> str | None:
@@ -40,6 +41,7 @@ def build(reference_root: str | None = None) -> None:
     reference_root = reference_root or _find_reference()
     if reference_root:
         args.append(f"REFERENCE_ROOT={reference_root}")
+        args.append("refgpu")      # the reference's GPU kernel recompiled for sm_100a: the benchmark's same-box comparison
     subprocess.run(args, check=True)
 
 
@@ -74,6 +76,25 @@ def lib():
 
 def have_ref() -> bool:
     return os.path.exists(_REF_SO)
+
+
+_ref_gpu = None
+
+
+def have_ref_gpu() -> bool:
+    return os.path.exists(_REF_GPU_SO)
+
+
+def ref_gpu():
+    """The reference's own GPU launcher (fp_eXmY_linear_kernel, fp6_llm/csrc/fp6_linear.cuh:20-32) recompiled for sm_100a:
+    ref_gpu().ref_gpu_linear(e, m, stream, weight, scales, act, out, M, N, K, workspace, split_k) on device pointers."""
+    global _ref_gpu
+    if _ref_gpu is None:
+        _ref_gpu = _load(_REF_GPU_SO)
+        vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+        _ref_gpu.ref_gpu_linear.restype = ci
+        _ref_gpu.ref_gpu_linear.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, ci]
+    return _ref_gpu
 
 
 def ref():
