@@ -108,6 +108,7 @@ const char* fp6b200_error_string(int code) { return cudaGetErrorString(static_ca
 int fp6b200_set_option(int option, int value) {
     if (option == FP6B200_OPTION_STATIC_WEIGHTS) fpx::set_weights_static(value);
     else if (option == FP6B200_OPTION_PROGRAMMATIC_LAUNCH) fpx::set_programmatic_launch(value);
+    else if (option == FP6B200_OPTION_PAIR_TILES) fpx::set_pair_tiles(value);
     else return cudaErrorInvalidValue;
     return cudaSuccess;
 }
@@ -115,6 +116,7 @@ int fp6b200_set_option(int option, int value) {
 int fp6b200_get_option(int option) {
     if (option == FP6B200_OPTION_STATIC_WEIGHTS) return fpx::weights_static();
     if (option == FP6B200_OPTION_PROGRAMMATIC_LAUNCH) return fpx::programmatic_launch();
+    if (option == FP6B200_OPTION_PAIR_TILES) return fpx::pair_tiles();
     return -1;
 }
 

@@ -98,13 +98,26 @@ struct RawBlock {
 // (positions past the end of a tile's K range exist too: they take part in the hand-shakes and are unpacked from
 // whatever the stage holds, but get no MMA).  Position p lives in ring slot p % a_slots.  Unpack group g (four warps,
 // one per tensor-memory lane quadrant) takes the positions p = g (mod 4); issuing warp i takes p = i (mod issuers).
-template <int BW, int N_TILE>
+// PAIR: two CTAs on neighbouring SMs (a cluster of two) work on one 256-row tile: each unpacks its own 128 rows into its
+// own tensor memory and loads HALF of the activation tile (N_TILE / 2 token rows); the first CTA issues
+// tcgen05.mma.cta_group::2 for both (M = 256), whose B operand is read from both shared memories.  The activation tile,
+// which a wide tile otherwise re-reads from L2 for every 128 output channels, is read once per 256.
+// Correct (tests) but NOT the default: on the 57344 x 8192 layer at 1024 tokens it takes 1.53 ms against 0.92 ms.  The
+// L2 -> SM traffic does fall (7.5 -> 5.2 GB) and no role is short of work; the pair's MMAs themselves complete only every
+// ~470 cycles instead of 128 (tensor pipe 30 % active, every hand-shake waiting on the previous MMAs), with 4 as with 8
+// ring slots.  FP6B200_OPTION_PAIR_TILES turns it on.
+template <int BW, int N_TILE, bool PAIR = false>
 struct Config {
     using Raw = RawBlock<BW>;
+    static constexpr bool pair = PAIR;
+    static constexpr int n_local = PAIR ? N_TILE / 2 : N_TILE;   // token rows of the activation tile in this CTA's shared memory
     static constexpr int ks = gemm_ks(N_TILE);
     static constexpr int kpw = N_TILE <= 128 ? 2 : 1;
-    static constexpr int stages = ks == 4 ? (N_TILE <= 16 ? 6 : 4) : 4;
-    static constexpr int a_slots = 4;   // one slot per unpack group: 4 x 64 columns of fp16 weights, 4 x 32 for the widest tile
+    // A pair signals across two SMs (stored slots and landed activations go to the first CTA's barriers, completed MMAs come
+    // back by a multicast commit), so its rings are twice as deep - which the halved activation tile and the 128
+    // tensor-memory columns the widest tile leaves free pay for.
+    static constexpr int stages = PAIR ? 8 : (ks == 4 ? (N_TILE <= 16 ? 6 : 4) : 4);
+    static constexpr int a_slots = PAIR ? 8 : 4;   // one or two slots per unpack group: 64 columns of fp16 weights each, 32 for the widest tile
     static constexpr int pos_per_stage = ks / kpw;
     // When every stage is one position and the two rings are equally deep, slot and stage coincide and ONE commit of the
     // issuing warp frees both the tensor-memory slot and the stage's activations (measured 6 % faster on the widest
@@ -132,7 +145,7 @@ struct Config {
     static constexpr uint32_t poll_issuer = N_TILE <= 64 ? kPollIssuerNarrow : kPollWide;
     // the unpack warps of a wide tile are ahead of the tensor pipe most of the time: every poll they save is power for it
     static constexpr uint32_t poll_unpack = N_TILE <= 128 ? ptx::kPollFast : kPollUnpackWide;
-    static constexpr uint32_t b_block = (uint32_t)N_TILE * 128u;
+    static constexpr uint32_t b_block = (uint32_t)n_local * 128u;
     static constexpr uint32_t w_off = ks * b_block;
     static constexpr uint32_t off1 = w_off;
     static constexpr uint32_t off2 = off1 + 2u * ks * Raw::seg1;
@@ -143,9 +156,12 @@ struct Config {
     static constexpr uint32_t acc_stride = N_TILE < 32 ? 32u : (uint32_t)N_TILE;
     static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
     static_assert(acc_col0 + issuers * acc_stride <= kTmemCols, "tensor memory budget");
-    static constexpr int num_barriers = 4 * stages + 2 * a_slots + 2;
-    static constexpr uint32_t smem_bytes = stages * stage_bytes + num_barriers * 8u + 32u;
+    // + for a pair: the peer's "activations landed" per stage, "slot stored" per slot and "accumulator read" words
+    static constexpr int num_barriers = 4 * stages + 2 * a_slots + 2 + (PAIR ? stages + a_slots + 1 : 0);
+    static constexpr uint32_t used_bytes = stages * stage_bytes + num_barriers * 8u + 32u;
+    static constexpr uint32_t smem_bytes = used_bytes > 116u * 1024u ? used_bytes : 116u * 1024u;   // never two CTAs per SM
     static_assert(2u * smem_bytes > 228u * 1024u, "two CTAs must never share an SM: each takes all of tensor memory");
+    static_assert(!PAIR || (issuers == 1 && N_TILE % 32 == 0), "a pair has one issuing thread");
     static_assert(smem_bytes <= 227u * 1024u, "shared memory budget");
 };
 
@@ -191,12 +207,12 @@ struct Params {
     int* status;
 };
 
-template <int E_BITS, int M_BITS, int N_TILE>
+template <int E_BITS, int M_BITS, int N_TILE, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ Params p) {
     constexpr int BW = 1 + E_BITS + M_BITS;
     constexpr bool kShortUnpack = M_BITS == 2 && (E_BITS == 3 || E_BITS == 2);   // e3m2, e2m2: the multiply-based sequence
-    using Cfg = Config<BW, N_TILE>;
+    using Cfg = Config<BW, N_TILE, PAIR>;
     using Raw = typename Cfg::Raw;
     constexpr int KS = Cfg::ks;
     constexpr int R = Cfg::stages;
@@ -216,12 +232,19 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     const uint32_t a_empty = a_full + 8 * SA;            // per slot: the MMAs that read it are done
     const uint32_t acc_full = a_empty + 8 * SA;
     const uint32_t acc_empty = acc_full + 8;
+    // pair only, used in the first CTA: what the second CTA reports (its half of the stage's activations has landed, its
+    // unpack warps have stored the slot, its epilogue warps have read the accumulator)
+    const uint32_t b_peer = acc_empty + 8;
+    const uint32_t a_peer = b_peer + 8 * R;
+    const uint32_t acc_peer = a_peer + 8 * SA;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_dyn + R * Cfg::stage_bytes + 8 * Cfg::num_barriers);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t cta = blockIdx.x;
+    // a pair shares one entry of the work plan; `half_id` is the CTA's place in it (its 128 of the tile's 256 rows)
+    const uint32_t half_id = PAIR ? ptx::cluster_ctarank() : 0u;
+    const uint32_t cta = PAIR ? blockIdx.x >> 1 : blockIdx.x;
     const WorkPlan& plan = p.plan;   // stays in the parameter space (it carries a table indexed by CTA)
 
     // The reduction / fix-up kernel that may follow is launched with programmatic stream serialisation: let it
@@ -243,13 +266,23 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         }
         for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, 4); ptx::mbar_init(a_empty + 8 * i, 1); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
+        if constexpr (PAIR) {
+            for (int i = lane; i < R; i += 32) ptx::mbar_init(b_peer + 8 * i, 1);
+            for (int i = lane; i < SA; i += 32) ptx::mbar_init(a_peer + 8 * i, 4);
+            if (lane == 0) ptx::mbar_init(acc_peer, kEpilogueWarps);
+        }
         if (lane == 0) *abort_word = 0;
         ptx::fence_barrier_init();
         if (lane == 0) ptx::prefetch_tensormap(&act_map);
     }
     if (warp == 0) {
-        ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTmemCols);
-        ptx::tmem_relinquish();
+        if constexpr (PAIR) {
+            ptx::tmem_alloc_pair(ptx::smem_u32(tmem_holder), kTmemCols);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTmemCols);
+            ptx::tmem_relinquish();
+        }
     }
     const bool is_producer = (warp >= kProducerWarp && warp < kProducerWarp + kProducerWarps) || warp == kActProducerWarp;
     if (is_producer) {
@@ -261,6 +294,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
         ptx::tc_fence_after_sync();
     }
+    if constexpr (PAIR) ptx::cluster_sync_all();   // both CTAs' barriers exist before either signals the other's
     if (threadIdx.x == 0) PROF_STAMP(1);
     const uint32_t tmem_base = *tmem_holder;   // valid for every warp but the producers, which never use it
 
@@ -290,9 +324,11 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             PROF_DECL
             plan_start(plan, cta, &iter);
             while (ok && plan_next(plan, cta, &iter, &seg)) {
-                const uint32_t m_tile = plan.n_tiles == 1 ? seg.tile : seg.tile / plan.n_tiles;
+                const uint32_t p_tile = plan.n_tiles == 1 ? seg.tile : seg.tile / plan.n_tiles;   // row tile of the plan (256 rows for a pair)
+                const uint32_t m_tile = PAIR ? 2u * p_tile + half_id : p_tile;                        // this CTA's 128 rows
                 const uint64_t blk0 = ((uint64_t)m_tile * 2 + half) * kblocks + seg.kb_begin;   // my row block, first K block
-                const int32_t n0 = (int32_t)((seg.tile - m_tile * plan.n_tiles) * N_TILE);
+                // a pair splits the tile's token rows: this CTA copies its half
+                const int32_t n0 = (int32_t)((seg.tile - p_tile * plan.n_tiles) * N_TILE + half_id * Cfg::n_local);
                 const uint32_t nstages = (seg.nkb + KS - 1) / KS;
                 uint32_t sidx = plan_first_stage(cta, nstages);   // stage of the segment's K range handled next
                 if (warp == kProducerWarp && issued == 0) PROF_STAMP(14);
@@ -341,7 +377,10 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         // stage, each as soon as its slot of the tensor-memory ring is full, and accumulates them in its own
         // accumulator); then all four warps, one per tensor-memory lane quadrant, read the accumulators, add them and
         // store the tile (lane = output channel, column = token).
-        constexpr uint32_t idesc = ptx::idesc_f16_f32(kTileM, N_TILE);
+        constexpr uint32_t idesc = ptx::idesc_f16_f32(PAIR ? 2 * kTileM : kTileM, N_TILE);
+        // In a pair the first CTA issues for both; the issuing thread of the second only passes on, stage by stage, that
+        // its half of the activations has landed.
+        const bool relay = PAIR && half_id != 0u;
         const uint32_t me = (uint32_t)warp;
         const int q = warp & 3;
         const uint64_t b_desc0 = ptx::smem_desc_k_sw128(ring);
@@ -355,7 +394,11 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         while (ok && plan_next(plan, cta, &iter, &seg)) {
             const uint32_t nstages = (seg.nkb + KS - 1) / KS;
             if (me < (uint32_t)NI && lane == 0) {
-                if (!PROF_WAIT(2, ptx::mbar_wait(acc_empty, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty))) ok = false;
+                if (!relay) {
+                    if (!PROF_WAIT(2, ptx::mbar_wait(acc_empty, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty))) ok = false;
+                    if constexpr (PAIR)
+                        if (ok && !ptx::mbar_wait(acc_peer, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty)) ok = false;
+                }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + Cfg::acc_col0 + me * Cfg::acc_stride;
                 constexpr uint32_t PPS = (uint32_t)Cfg::pos_per_stage, IST = (uint32_t)Cfg::issuer_step, KPW = (uint32_t)Cfg::kpw;
@@ -375,10 +418,20 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     sidx += IST;
                     if (!PROF_WAIT(1, ptx::mbar_wait(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
+                    if constexpr (PAIR) {
+                        if (relay) {
+                            ptx::mbar_arrive_remote(ptx::mapa(b_peer + 8 * rp.idx, 0u));
+                            rp.advance(IST);
+                            continue;
+                        }
+                        if (!PROF_WAIT(2, ptx::mbar_wait(b_peer + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                    }
                     const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::stage_bytes >> 4));
 #pragma unroll
                     for (uint32_t sub = sub0; sub < PPS; sub += (uint32_t)NI) {
                         if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull, Cfg::poll_issuer))) { ok = false; break; }
+                        if constexpr (PAIR)
+                            if (!PROF_WAIT(4, ptx::mbar_wait(a_peer + 8 * ap.idx, ap.lap, abort_word, kErrAFull, Cfg::poll_issuer))) { ok = false; break; }
                         if (me == 0 && nseg == 0 && t == 0) PROF_STAMP(5);
                         PROF_BEGIN(t_issue)
                         ptx::tc_fence_after_sync();
@@ -389,24 +442,35 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                             if (kbi < cnt) {
 #pragma unroll
                                 for (uint32_t kk = 0; kk < 4; kk++) {   // four K=16 steps; B advances 32 bytes inside the swizzle row
-                                    ptx::mma_f16_ts(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
-                                                    b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
+                                    if constexpr (PAIR)
+                                        ptx::mma_f16_ts_pair(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
+                                                             b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
+                                    else
+                                        ptx::mma_f16_ts(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
+                                                        b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
                                     accumulate = 1u;
                                 }
                             }
                         }
                         PROF_END(3, t_issue)
                         PROF_BEGIN(t_commit)
-                        ptx::tc_commit(a_empty + 8 * ap.idx);
+                        if constexpr (PAIR) ptx::tc_commit_pair(a_empty + 8 * ap.idx);
+                        else ptx::tc_commit(a_empty + 8 * ap.idx);
                         PROF_END(4, t_commit)
                         ap.advance(NI);
                     }
                     if (!ok) break;
-                    if (!Cfg::unified) ptx::tc_commit(b_empty + 8 * rp.idx);
+                    if (!Cfg::unified) {
+                        if constexpr (PAIR) ptx::tc_commit_pair(b_empty + 8 * rp.idx);
+                        else ptx::tc_commit(b_empty + 8 * rp.idx);
+                    }
                     if (me == 0) PROF_STAMP(6);
                     rp.advance(IST);
                 }
-                if (ok) ptx::tc_commit(acc_full);   // arrives once this issuer's MMAs (if any) are done
+                if (ok && !relay) {   // arrives once this issuer's MMAs (if any) are done
+                    if constexpr (PAIR) ptx::tc_commit_pair(acc_full);
+                    else ptx::tc_commit(acc_full);
+                }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
@@ -431,7 +495,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             }
             j0 += nstages;
 
-            const uint32_t m_tile = plan.n_tiles == 1 ? seg.tile : seg.tile / plan.n_tiles, n_tile = seg.tile - m_tile * plan.n_tiles;
+            const uint32_t p_tile = plan.n_tiles == 1 ? seg.tile : seg.tile / plan.n_tiles, n_tile = seg.tile - p_tile * plan.n_tiles;
+            const uint32_t m_tile = PAIR ? 2u * p_tile + half_id : p_tile;   // this CTA's 128 rows of the plan's row tile
             const uint32_t row_in_tile = 32u * q + lane;
             const uint32_t row = m_tile * kTileM + row_in_tile;
             // the accumulator holds sum(x * pattern); pattern = code value / 2^bias, so scale by 2^bias * scale[row] here, in fp32
@@ -490,16 +555,18 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
 #pragma unroll
                     for (int u = 0; u < CH; u++)
                         if (n0 + u < p.N) dst[(size_t)u * p.M] = f[u] * row_scale;
-                } else {
-                    float* dst = p.workspace + ((size_t)seg.out_index * N_TILE + c0) * kTileM + row_in_tile;
+                } else {   // a pair's slot holds the 256 rows of the plan's tile: each CTA its half
+                    constexpr uint32_t kSlotRows = PAIR ? 2u * kTileM : (uint32_t)kTileM;
+                    float* dst = p.workspace + ((size_t)seg.out_index * N_TILE + c0) * kSlotRows + half_id * kTileM + row_in_tile;
 #pragma unroll
                     for (int u = 0; u < CH; u++)
-                        if (n0 + u < p.N) dst[u * kTileM] = f[u] * row_scale;
+                        if (n0 + u < p.N) dst[u * kSlotRows] = f[u] * row_scale;
                 }
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            ptx::mbar_arrive_elected(acc_empty);
+            if (PAIR && half_id != 0u) ptx::mbar_arrive_remote_elected(ptx::mapa(acc_peer, 0u));   // tell the issuing CTA
+            else ptx::mbar_arrive_elected(acc_empty);
             if (threadIdx.x == 0) PROF_STAMP(8);
             nseg++;
         }
@@ -554,7 +621,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             ptx::tc_wait_st();
             ptx::tc_fence_before_sync();
             __syncwarp();
-            ptx::mbar_arrive_elected(pending_bar);
+            if (PAIR && half_id != 0u) ptx::mbar_arrive_remote_elected(pending_bar);   // a barrier of the issuing CTA
+            else ptx::mbar_arrive_elected(pending_bar);
             pending_bar = 0;
         };
         while (ok && plan_next(plan, cta, &iter, &seg)) {
@@ -603,7 +671,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock + (16u << 16), v[1]);
                 }
                 if (!ok) break;
-                pending_bar = a_full + 8 * slot;
+                pending_bar = (PAIR && half_id != 0u) ? ptx::mapa(a_peer + 8 * slot, 0u) : a_full + 8 * slot;
                 hand_over();
                 slot += kDequantGroups;
                 if (slot >= (uint32_t)SA) { slot -= SA; slot_lap ^= 1u; }
@@ -617,6 +685,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     // ------------------------------------------------------------ teardown
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) ptx::cluster_sync_all();   // neither CTA leaves while the other may still signal its barriers
     if (warp == 0) {
         if (*abort_word != 0 && lane == 0) {   // gave up: let MMAs that may still be in flight finish before freeing
             const uint64_t t0 = ptx::global_timer_ns();
@@ -624,7 +693,8 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         }
         __syncwarp();
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (PAIR) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+        else ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_word != 0) atomicCAS(p.status, 0, *abort_word);
     if (threadIdx.x == 0) PROF_STAMP(9);
@@ -676,7 +746,8 @@ constexpr uint64_t kFixupCostUnits = 20;   // the fix-up launch and its dependen
 constexpr uint64_t kMinUnitsPerCta = 8;   // a CTA is not started for fewer 64-K blocks than this (two 256-K stages)
 __global__ void __launch_bounds__(kFixupThreads) streamk_fixup_kernel(const __grid_constant__ OutTargets out, const float* __restrict__ slots,
                                                                          uint32_t N, int n_tile_size, const __grid_constant__ WorkPlan plan,
-                                                                         int early_trigger, const __half* __restrict__ bias, int activation, uint32_t groups) {
+                                                                         int early_trigger, const __half* __restrict__ bias, int activation, uint32_t groups,
+                                                                         uint32_t tile_rows) {
     __shared__ uint32_t cand_slot[kMaxGrid];   // per candidate CTA: its slot, or ~0u when it holds nothing
     __shared__ uint32_t part_slot[kMaxGrid];   // slots that hold a part of this tile, in CTA order
     __shared__ uint32_t part_count;
@@ -707,7 +778,9 @@ __global__ void __launch_bounds__(kFixupThreads) streamk_fixup_kernel(const __gr
     __syncthreads();
     const uint32_t count = part_count;
     const uint32_t row4 = (threadIdx.x & 31u) * 4u;          // first of this thread's four output channels
-    const size_t slot_stride = (size_t)n_tile_size * kTileM;
+    // the plan's row tiles are tile_rows high (256 when CTA pairs computed them); blockIdx.z picks the 128 rows of this CTA
+    const size_t slot_stride = (size_t)n_tile_size * tile_rows;
+    const uint32_t row_off = blockIdx.z * kTileM + row4;
     asm volatile("griddepcontrol.wait;" ::: "memory");       // the GEMM grid has completed and its stores are visible
     if (threadIdx.x == 0 && blockIdx.y == 0) PROF_STAMP(11);
     __shared__ float4 group_sum[16][32];                      // [group * cols + column][lane]
@@ -718,7 +791,7 @@ __global__ void __launch_bounds__(kFixupThreads) streamk_fixup_kernel(const __gr
     const bool live = c < (uint32_t)n_tile_size && n < N;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live) {
-        const float* base = slots + (size_t)c * kTileM + row4;
+        const float* base = slots + (size_t)c * tile_rows + row_off;
 #pragma unroll 8
         for (uint32_t i = grp; i < count; i += groups) {
             const float4 v = *reinterpret_cast<const float4*>(base + part_slot[i] * slot_stride);
@@ -732,7 +805,7 @@ __global__ void __launch_bounds__(kFixupThreads) streamk_fixup_kernel(const __gr
             const float4 v = group_sum[g * cols + col][threadIdx.x & 31u];
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        const uint32_t m0 = m_tile * kTileM + row4;
+        const uint32_t m0 = m_tile * tile_rows + row_off;
         if (bias) {
             acc.x += __half2float(bias[m0]); acc.y += __half2float(bias[m0 + 1]);
             acc.z += __half2float(bias[m0 + 2]); acc.w += __half2float(bias[m0 + 3]);
@@ -866,10 +939,10 @@ int make_plan(size_t M, size_t n_tiles, size_t K, int split_k, int sms, WorkPlan
 
 namespace {
 
-template <int E_BITS, int M_BITS, int N_TILE>
+template <int E_BITS, int M_BITS, int N_TILE, bool PAIR = false>
 cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
-    auto kernel = fpx_gemm_kernel<E_BITS, M_BITS, N_TILE>;
-    constexpr uint32_t smem = Config<1 + E_BITS + M_BITS, N_TILE>::smem_bytes;
+    auto kernel = fpx_gemm_kernel<E_BITS, M_BITS, N_TILE, PAIR>;
+    constexpr uint32_t smem = Config<1 + E_BITS + M_BITS, N_TILE, PAIR>::smem_bytes;
     static std::atomic<bool> configured[64];   // zero-initialised; several host threads may launch at once
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
@@ -882,20 +955,28 @@ cudaError_t launch_one(cudaStream_t stream, const CUtensorMap& map, const Params
     // Programmatic launch: the CTAs may start, set up and find their work while the previous kernel of the stream is
     // still finishing; every role waits (griddepcontrol.wait) before it first touches global memory.
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(prm.plan.grid);
+    cfg.gridDim = dim3(PAIR ? 2 * prm.plan.grid : prm.plan.grid);   // a pair of CTAs (a cluster of two) per entry of the plan
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = programmatic_launch() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (PAIR) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     return cudaLaunchKernelEx(&cfg, kernel, map, prm);
 }
 
 template <int E_BITS, int M_BITS>
-cudaError_t launch_by_n(int n_tile, cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
+cudaError_t launch_by_n(int n_tile, bool pair, cudaStream_t stream, const CUtensorMap& map, const Params& prm) {
+    if (pair) return launch_one<E_BITS, M_BITS, 256, true>(stream, map, prm);
     switch (n_tile) {
         case 16:  return launch_one<E_BITS, M_BITS, 16>(stream, map, prm);
         case 32:  return launch_one<E_BITS, M_BITS, 32>(stream, map, prm);
@@ -928,12 +1009,27 @@ int device_sm_count() {
     return n;
 }
 
+static std::atomic<int> g_pair_tiles{0};   // off: measured 0.6 of the single-CTA speed (see Config)
+void set_pair_tiles(int on) { g_pair_tiles.store(on < 0 ? 0 : (on > 2 ? 2 : on)); }   // 2: also for layers too small to occupy every pair
+int pair_tiles() { return g_pair_tiles.load(); }
+
+// Whether a call runs as CTA pairs on 256-row tiles (the widest tile only, the library's own decomposition, enough row
+// tiles to occupy the pairs), and its plan: for a pair the plan's row tiles are 256 rows and its "CTAs" are pairs.
+static int plan_call(size_t M, size_t N, size_t K, int split_k, bool has_targets, WorkPlan* plan, bool* pair) {
+    const int n_tile = gemm_n_tile(N);
+    const size_t n_tiles = (N + n_tile - 1) / n_tile;
+    const int sms = device_sm_count() < (int)kMaxGrid ? device_sm_count() : (int)kMaxGrid;
+    *pair = pair_tiles() && n_tile == 256 && split_k == 0 && !has_targets && sms >= 2 &&
+            (pair_tiles() == 2 || (M / 256) * n_tiles >= (size_t)(sms / 2));
+    if (*pair) return make_plan(M / 2, n_tiles, K, split_k, sms / 2, plan);   // M / 2 rows in 128-row tiles = M in 256-row tiles
+    return make_plan(M, n_tiles, K, split_k, sms, plan);
+}
+
 int gemm_kernel_launches(size_t M, size_t N, size_t K, int split_k) {
     if (M == 0 || M % 256 != 0 || K == 0 || K % 64 != 0 || N == 0 || split_k < 0) return 0;
-    const int n_tile = gemm_n_tile(N);
-    const int sms = device_sm_count() < (int)kMaxGrid ? device_sm_count() : (int)kMaxGrid;
     WorkPlan plan;
-    const int eff_split = make_plan(M, (N + n_tile - 1) / n_tile, K, split_k, sms, &plan);
+    bool pair = false;
+    const int eff_split = plan_call(M, N, K, split_k, false, &plan, &pair);
     if (plan.mode == kStreamK) return plan_rem_tiles(plan) ? 2 : 1;   // GEMM (+ fix-up of the split tiles)
     return eff_split > 1 ? 2 : 1;                                     // GEMM (+ split-K reduction)
 }
@@ -973,7 +1069,7 @@ int programmatic_launch() { return g_programmatic_launch.load(); }
 
 // Sums the partial tiles a stream-K GEMM left in its slots (launched programmatically after it).
 cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, const float* workspace, size_t N,
-                                 int n_tile, const WorkPlan& plan, const Epilogue* epilogue) {
+                                 int n_tile, const WorkPlan& plan, const Epilogue* epilogue, int tile_rows) {
     const uint32_t rem = plan_rem_tiles(plan);
     if (rem == 0) return cudaSuccess;
     // groups: as many as half the parts of a tile (about grid / rem CTAs share one), while the grid stays within ~2 CTAs per SM
@@ -984,7 +1080,7 @@ cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, c
         groups *= 2;
     const uint32_t cols = 16 / groups;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rem, (unsigned)((n_tile + cols - 1) / cols));
+    cfg.gridDim = dim3(rem, (unsigned)((n_tile + cols - 1) / cols), (unsigned)(tile_rows / kTileM));
     cfg.blockDim = dim3(kFixupThreads);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -995,7 +1091,8 @@ cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, c
     const int early = programmatic_launch() ? 1 : 0;
     const __half* bias = epilogue ? epilogue->bias : nullptr;
     const int activation = epilogue ? epilogue->activation : kActNone;
-    return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, workspace, (uint32_t)N, n_tile, plan, early, bias, activation, groups);
+    return cudaLaunchKernelEx(&cfg, streamk_fixup_kernel, where, workspace, (uint32_t)N, n_tile, plan, early, bias, activation, groups,
+                              (uint32_t)tile_rows);
 }
 
 cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void* weight, const __half* scales,
@@ -1033,12 +1130,14 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     const int n_tile = gemm_n_tile(N);
     const size_t n_tiles = (N + n_tile - 1) / n_tile;
     if ((M / kTileM) * n_tiles > 0x3fffffffull) return cudaErrorInvalidValue;
+    Params prm;
+    WorkPlan& plan = prm.plan;
+    bool pair = false;
+    const int eff_split = plan_call(M, N, K, split_k, targets != nullptr, &plan, &pair);
     CUtensorMap map;
-    cudaError_t err = make_act_map(&map, act, N, K, n_tile, gemm_ks(n_tile));
+    cudaError_t err = make_act_map(&map, act, N, K, pair ? n_tile / 2 : n_tile, gemm_ks(n_tile));   // a pair's CTAs copy half a tile each
     if (err != cudaSuccess) return err;
 
-    const int sms = device_sm_count() < (int)kMaxGrid ? device_sm_count() : (int)kMaxGrid;
-    Params prm;
     prm.weight = static_cast<const uint8_t*>(weight);
     {
         const int bw_ = 1 + e_bits + m_bits;
@@ -1058,14 +1157,12 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
     prm.N = (uint32_t)N;
     prm.K = (uint32_t)K;
     prm.status = status;
-    WorkPlan& plan = prm.plan;
-    const int eff_split = make_plan(M, n_tiles, K, split_k, sms, &plan);
-    FPX_DISPATCH_FORMAT(e_bits, m_bits, (err = launch_by_n<kE, kM>(n_tile, stream, map, prm)));
+    FPX_DISPATCH_FORMAT(e_bits, m_bits, (err = launch_by_n<kE, kM>(n_tile, pair, stream, map, prm)));
     if (err != cudaSuccess) return err;
     if (plan.mode == kStreamK) {
         const uint32_t rem = plan_rem_tiles(plan);
         if (rem == 0) return cudaSuccess;
-        return launch_streamk_fixup(stream, where, workspace, N, n_tile, plan, epilogue);
+        return launch_streamk_fixup(stream, where, workspace, N, n_tile, plan, epilogue, pair ? 2 * kTileM : kTileM);
     }
     if (eff_split > 1) return launch_splitk_reduce(stream, out, workspace, M * N, eff_split, true, M, epilogue);
     return cudaSuccess;

@@ -61,8 +61,9 @@ cudaError_t launch_gemm(int e_bits, int m_bits, cudaStream_t stream, const void*
 // split_k >= 1 the caller's.  Returns the effective split.
 struct WorkPlan;
 int make_plan(size_t M, size_t n_tiles, size_t K, int split_k, int sms, WorkPlan* out);
+// tile_rows: height of the plan's row tiles (128, or 256 when CTA pairs computed them)
 cudaError_t launch_streamk_fixup(cudaStream_t stream, const OutTargets& where, const float* workspace, size_t N,
-                                 int n_tile, const WorkPlan& plan, const Epilogue* epilogue);
+                                 int n_tile, const WorkPlan& plan, const Epilogue* epilogue, int tile_rows = 128);
 // Cross-GPU arrival barrier that ends a sharded layer: tells every peer that this rank's stores into its output
 // buffer are complete and waits (bounded) for the same word from every peer.  flag_peers[r] = rank r's flag array
 // (one 32-bit word per rank) as mapped here; epoch_counter = this rank's own call counter in device memory.
@@ -79,6 +80,10 @@ int weights_static();
 // whether the fix-up kernel lets the kernel after it do the same.  On by default.
 void set_programmatic_launch(int on);
 int programmatic_launch();
+// Whether layers of more than 128 tokens run as pairs of CTAs on 256-row tiles (tcgen05 cta_group::2): 0 no (default: it
+// measured slower), 1 when the layer has a tile for every pair, 2 always.
+void set_pair_tiles(int on);
+int pair_tiles();
 int gemm_n_tile(size_t N);
 // Kernels one GEMM call launches on the current device (0 for an invalid shape).
 int gemm_kernel_launches(size_t M, size_t N, size_t K, int split_k);

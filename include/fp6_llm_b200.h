@@ -235,9 +235,13 @@ int fp6b200_linear_gather(int e_bits, int m_bits, void* stream, const void* weig
  * it starts and sets itself up while the previous kernel of the stream is finishing (it still waits for that kernel
  * to complete before it touches memory the kernel may have written).  0 restores plain stream order between a GEMM
  * and whatever precedes it.
+ * FP6B200_OPTION_PAIR_TILES (default 0): layers of more than 128 tokens run as pairs of CTAs on neighbouring SMs that share
+ * one 256-row tile and each load half of its activation tile (tcgen05 cta_group::2); 1 = when the layer has a tile for
+ * every pair, 2 = always.  Same results; off by default because it measured slower than one CTA per tile.
  */
 #define FP6B200_OPTION_STATIC_WEIGHTS 1
 #define FP6B200_OPTION_PROGRAMMATIC_LAUNCH 2
+#define FP6B200_OPTION_PAIR_TILES 3
 int fp6b200_set_option(int option, int value);
 int fp6b200_get_option(int option);
 

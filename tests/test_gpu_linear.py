@@ -224,3 +224,26 @@ def test_long_k_repeated_launches_stay_exact_per_tile(native_lib, oc, ic, bs):
         rel = err.norm(dim=1) / refg.norm(dim=1)
         assert rel.max().item() <= 2e-3, (rel.argmax().item(), rel.max().item())
         assert torch.equal(y, outs[0])                                            # and the launches agree bit for bit
+
+
+@pytest.mark.parametrize("oc,ic,bs", [(512, 256, 200), (1024, 2048, 300), (4096, 1024, 512)])
+def test_cta_pair_tiles_give_the_same_layer(oracle_mod, native_lib, oc, ic, bs):
+    """FP6B200_OPTION_PAIR_TILES: two CTAs share a 256-row tile (cta_group::2 MMAs, half of the activation tile each).
+    Same tolerances against the oracle; the option is restored afterwards."""
+    import fp6_llm_b200 as f
+    from fp6_llm_b200.formats import random_codes_layer
+    w, s = random_codes_layer(oc, ic, 3, 2, seed=oc + bs, scale_lo=0.005, scale_hi=0.02)
+    x = torch.randn(bs, ic, generator=torch.Generator().manual_seed(2)).half()
+    packed = f.weight_prepacking_eXmY_cpu(3, 2, w.cuda())
+    truth = oracle_mod.linear(x.numpy(), w.numpy(), s.numpy(), 3, 2)
+    before = native_lib.fp6b200_get_option(3)
+    try:
+        assert native_lib.fp6b200_set_option(3, 2) == 0
+        y = f.linear_forward_eXmY_cuda(3, 2, x.cuda(), packed, s.cuda(), 0)
+        assert f.device_status() == 0
+    finally:
+        native_lib.fp6b200_set_option(3, before)
+    res = oracle_mod.check_tolerance(y.float().cpu().numpy(), truth)
+    assert res["ok"], res
+    plain = f.linear_forward_eXmY_cuda(3, 2, x.cuda(), packed, s.cuda(), 0)
+    assert (y.float() - plain.float()).abs().max().item() <= 2e-3 * plain.float().abs().max().item()
