@@ -29,7 +29,7 @@ C_SYMBOLS = (
     "fp6b200_device_status", "fp6b200_linear_static_scratch", "fp6b200_static_scratch_bytes",
     "fp6b200_linear_gather", "fp6b200_set_option", "fp6b200_get_option", "fp6b200_quantize_prepack",
     "fp6b200_linear_host_io_batch", "fp6b200_kernel_launches", "fp6b200_linear_ex",
-    "fp6b200_native_supported", "fp6b200_native_weight_bytes", "fp6b200_native_workspace_bytes",
+    "fp6b200_native_supported", "fp6b200_native_preferred", "fp6b200_native_weight_bytes", "fp6b200_native_workspace_bytes",
     "fp6b200_native_repack", "fp6b200_linear_native", "fp6b200_native_kernel_launches", "fp6b200_linear_native_gather",
 )
 
@@ -97,6 +97,8 @@ def lib() -> ctypes.CDLL:
     L.fp6b200_linear_ex.argtypes = [ci, ci, vp, vp, vp, vp, vp, sz, sz, sz, vp, ci, vp, ci]
     L.fp6b200_native_supported.restype = ci
     L.fp6b200_native_supported.argtypes = [ci, ci, sz, sz, sz]
+    L.fp6b200_native_preferred.restype = ci
+    L.fp6b200_native_preferred.argtypes = [ci, ci, sz, sz, sz]
     L.fp6b200_native_weight_bytes.restype = sz
     L.fp6b200_native_weight_bytes.argtypes = [sz, sz]
     L.fp6b200_native_workspace_bytes.restype = sz

@@ -156,6 +156,13 @@ int fp6b200_native_supported(int e_bits, int m_bits, size_t M, size_t N, size_t 
            N <= (size_t)fpx::native_max_tokens();
 }
 
+int fp6b200_native_preferred(int e_bits, int m_bits, size_t M, size_t N, size_t K) {
+    // measured on the LLaMA-2 7B / 13B / 70B layer sets: up to 32 tokens the tensor-core path makes the step faster (a rule
+    // that kept layers of 4096 output channels on the other kernel from 5 tokens on, as their isolated timings suggested,
+    // made the 7B step 4 % slower); from 33 tokens on four activation planes at the 8-bit rate cost more than unpacking
+    return fp6b200_native_supported(e_bits, m_bits, M, N, K) && N <= 32;
+}
+
 size_t fp6b200_native_weight_bytes(size_t M, size_t K) { return fpx::native_weight_bytes(M, K); }
 
 size_t fp6b200_native_workspace_bytes(size_t N, size_t K) { return fpx::native_workspace_bytes(N, K); }
@@ -298,7 +305,7 @@ cudaError_t batch_context(int n_calls, BatchContext** ctx) {
 
 // whether a call of a host batch runs on the tensor cores' own six-bit inputs
 static bool host_call_native(const fp6b200_host_call& c) {
-    return c.weight_native_dev && c.split_k == 0 && c.N <= 32 && fp6b200_native_supported(c.e_bits, c.m_bits, c.M, c.N, c.K);
+    return c.weight_native_dev && c.split_k == 0 && fp6b200_native_preferred(c.e_bits, c.m_bits, c.M, c.N, c.K);
 }
 
 int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls) {

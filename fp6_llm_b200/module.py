@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .formats import bit_width, check_format, magnitudes
-from .ops import (ACT_NONE, ACT_SILU_MUL, NATIVE_AUTO_MAX, interleave_gate_up, linear_forward_ex, linear_forward_native,
+from .ops import (ACT_NONE, ACT_SILU_MUL, interleave_gate_up, linear_forward_ex, linear_forward_native, native_preferred,
                   native_repack, native_supported, quantize_prepack_cuda)
 
 
@@ -23,7 +23,8 @@ def _enable_native(layer) -> None:
 
 def _forward(layer, flat: torch.Tensor, activation: int) -> torch.Tensor:
     native = getattr(layer, "weight_native", None)
-    if native is not None and flat.shape[0] <= NATIVE_AUTO_MAX and layer.split_k == 0:
+    if native is not None and layer.split_k == 0 and native_preferred(layer.e_bits, layer.m_bits, layer.weight.shape[0],
+                                                                      layer.in_features, flat.shape[0]):
         return linear_forward_native(layer.e_bits, layer.m_bits, flat, native, layer.scales, layer.bias, activation)
     # the bias is added inside the kernel's fp32 epilogue, before the one rounding to fp16
     return linear_forward_ex(layer.e_bits, layer.m_bits, flat, layer.weight, layer.scales, layer.split_k, layer.bias, activation)
@@ -73,7 +74,7 @@ class FPxLinear(torch.nn.Module):
 
     def enable_native(self) -> "FPxLinear":
         """Also keep the weights in the tile layout of the tensor cores' own six-bit inputs (6 more bits per weight,
-        whatever the format): batches of up to NATIVE_AUTO_MAX tokens run on that path, larger ones as before."""
+        whatever the format): batches for which `native_preferred` says so (decode sizes) run on that path, the others as before."""
         _enable_native(self)
         return self
 

@@ -157,12 +157,18 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------------------- the tensor cores' own six-bit inputs
 NATIVE_MAX_TOKENS = 64     # what linear_forward_native takes
-NATIVE_AUTO_MAX = 32       # up to this batch it measured faster than the fp16-pattern kernel on every LLaMA-2-70B layer
+NATIVE_AUTO_MAX = 32       # the largest batch for which it is ever chosen automatically (see native_preferred)
 
 
 def native_supported(EXPONENT: int, MANTISSA: int, OC: int, IC: int, B: int) -> bool:
     """Whether :func:`linear_forward_native` takes this format and shape (OC % 256 == 0, IC % 64 == 0, 1 <= B <= 64)."""
     return bool(_native.lib().fp6b200_native_supported(EXPONENT, MANTISSA, OC, B, IC))
+
+
+def native_preferred(EXPONENT: int, MANTISSA: int, OC: int, IC: int, B: int) -> bool:
+    """Whether :func:`linear_forward_native` measured faster than the fp16-pattern kernel for this shape (at most 32
+    tokens): the rule the modules and the sharded layer choose by."""
+    return bool(_native.lib().fp6b200_native_preferred(EXPONENT, MANTISSA, OC, B, IC))
 
 
 def native_repack(EXPONENT: int, MANTISSA: int, _weights: torch.Tensor) -> torch.Tensor:

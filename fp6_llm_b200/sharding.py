@@ -204,8 +204,8 @@ class ShardedFPxLinear:
                  native: bool = False):
         self.packed, self.scale, self.plan, self.rank = packed_shard, scale_shard, list(plan), rank
         self.e_bits, self.m_bits, self.group, self.exchange = e_bits, m_bits, group, exchange
-        # native=True: the shard is also kept in the tile layout of the tensor cores' own six-bit inputs, and batches of up
-        # to NATIVE_AUTO_MAX tokens run there
+        # native=True: the shard is also kept in the tile layout of the tensor cores' own six-bit inputs, and the batches for
+        # which ops.native_preferred says so run there
         self.native = None
         if native:
             from .ops import native_repack, native_supported
@@ -214,8 +214,11 @@ class ShardedFPxLinear:
                 self.native = native_repack(e_bits, m_bits, packed_shard)
 
     def use_native(self, batch: int, split_k: int) -> bool:
-        from .ops import NATIVE_AUTO_MAX
-        return self.native is not None and split_k == 0 and batch <= NATIVE_AUTO_MAX
+        from .ops import native_preferred
+        if self.native is None or split_k != 0:
+            return False
+        ic = self.packed.shape[1] * 32 // bit_width(self.e_bits, self.m_bits)
+        return native_preferred(self.e_bits, self.m_bits, self.packed.shape[0], ic, batch)
 
     def forward_local(self, x: torch.Tensor, split_k: int = 0) -> torch.Tensor:
         from .ops import linear_forward_eXmY_cuda, linear_forward_native

@@ -75,6 +75,9 @@ int fp6b200_linear_ex(int e_bits, int m_bits, void* stream, const void* weight_p
  *   fp6b200_linear_native          the layer; arguments as fp6b200_linear_ex, the library's own work decomposition.
  */
 int fp6b200_native_supported(int e_bits, int m_bits, size_t M, size_t N, size_t K);
+/* 1 where fp6b200_linear_native measured faster than fp6b200_linear (at most 32 tokens): what
+ * the module, the sharded layer and the batched host entry use to choose between the two. */
+int fp6b200_native_preferred(int e_bits, int m_bits, size_t M, size_t N, size_t K);
 size_t fp6b200_native_weight_bytes(size_t M, size_t K);
 size_t fp6b200_native_workspace_bytes(size_t N, size_t K);
 int fp6b200_native_repack(int e_bits, int m_bits, void* stream, const void* weight_packed, void* weight_native, size_t M,
@@ -114,7 +117,7 @@ typedef struct fp6b200_host_call {
     size_t M, N, K;
     int split_k;            /* as for fp6b200_linear; 0 = library decomposition */
     const void* weight_native_dev;   /* NULL, or the same weights in the layout of fp6b200_native_repack: calls with
-                                        split_k == 0 and N <= 32 that fp6b200_native_supported accepts then run on
+                                        split_k == 0 for which fp6b200_native_preferred says so then run on
                                         fp6b200_linear_native */
 } fp6b200_host_call;
 int fp6b200_linear_host_io_batch(const fp6b200_host_call* calls, int n_calls);
