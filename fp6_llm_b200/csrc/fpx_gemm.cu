@@ -102,10 +102,12 @@ struct RawBlock {
 // own tensor memory and loads HALF of the activation tile (N_TILE / 2 token rows); the first CTA issues
 // tcgen05.mma.cta_group::2 for both (M = 256), whose B operand is read from both shared memories.  The activation tile,
 // which a wide tile otherwise re-reads from L2 for every 128 output channels, is read once per 256.
-// Correct (tests) but NOT the default: on the 57344 x 8192 layer at 1024 tokens it takes 1.53 ms against 0.92 ms.  The
-// L2 -> SM traffic does fall (7.5 -> 5.2 GB) and no role is short of work; the pair's MMAs themselves complete only every
-// ~470 cycles instead of 128 (tensor pipe 30 % active, every hand-shake waiting on the previous MMAs), with 4 as with 8
-// ring slots.  FP6B200_OPTION_PAIR_TILES turns it on.
+// Correct (tests) but NOT the default: on the 57344 x 8192 layer at 1024 tokens it takes 1.53 ms against 0.92 ms, with 4 as
+// with 8 ring slots.  Measured: the pair's MMAs run at the full rate in isolation (128 cycles per M256 x N256 x K16, with
+// multicast commits and concurrent tensor-memory stores), the L2 -> SM traffic does fall (7.5 -> 5.2 GB), and every role
+// waits for the activation copies: a CTA's 16 KB boxes land one per ~1 us (16 GB/s per SM) where the single CTA's 32 KB
+// boxes land one per 0.6 us, whether the activations are read in the caller's layout or re-laid K block by K block.
+// FP6B200_OPTION_PAIR_TILES turns it on.
 template <int BW, int N_TILE, bool PAIR = false>
 struct Config {
     using Raw = RawBlock<BW>;
