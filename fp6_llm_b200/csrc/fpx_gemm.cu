@@ -189,6 +189,19 @@ __device__ unsigned long long g_stamp[160][16];   // global-timer stamps (ns) of
 #define PROF_FLUSH() do { } while (0)
 #endif
 
+// Optional timeline of the first CTA (build with -DFPX_TRACE): global-timer stamps of what each role sees and does for
+// the ring positions kTraceFirst .. kTraceFirst + 63, read back with fp6b200_debug_read_trace.
+#ifdef FPX_TRACE
+#ifndef FPX_TRACE_FIRST
+#define FPX_TRACE_FIRST 512
+#endif
+constexpr uint32_t kTraceFirst = FPX_TRACE_FIRST;
+__device__ unsigned long long g_trace[12][64];
+#define PROF_TRACE(role, pos) do { if (blockIdx.x == 0 && lane == 0 && (uint32_t)(pos) - kTraceFirst < 64u) g_trace[role][(uint32_t)(pos) - kTraceFirst] = ptx::global_timer_ns(); } while (0)
+#else
+#define PROF_TRACE(role, pos) do { } while (0)
+#endif
+
 constexpr uint32_t kMaxGrid = 256;   // CTAs the fix-up kernel's slot list can hold
 
 // silu(gate) * up in fp32
@@ -242,7 +255,9 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_dyn + R * Cfg::stage_bytes + 8 * Cfg::num_barriers);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
-    const int warp = threadIdx.x >> 5;
+    // the warp's index, taken through a shuffle so that the compiler knows it to be the same in every lane: the roles that
+    // a whole warp executes (MMA issue) then keep their addresses and descriptors warp-uniform
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     // a pair shares one entry of the work plan; `half_id` is the CTA's place in it (its 128 of the tile's 256 rows)
     const uint32_t half_id = PAIR ? ptx::cluster_ctarank() : 0u;
@@ -262,14 +277,16 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     if (warp == kProducerWarp) {   // one barrier per lane and round
         for (int i = lane; i < R; i += 32) {
             ptx::mbar_init(w_full + 8 * i, kProducerWarps);
-            ptx::mbar_init(b_full + 8 * i, 1);
+            // unified: "activations landed" and "slot stored" share the barrier (the copy's arrival + four unpack warps),
+            // so that the issuing warp waits once per position; the second CTA of a pair reports both to the first
+            ptx::mbar_init(b_full + 8 * i, Cfg::unified && half_id == 0u ? 5 : 1);
             ptx::mbar_init(w_empty + 8 * i, Cfg::readers);
             ptx::mbar_init(b_empty + 8 * i, Cfg::stage_issuers);
         }
         for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, 4); ptx::mbar_init(a_empty + 8 * i, 1); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
         if constexpr (PAIR) {
-            for (int i = lane; i < R; i += 32) ptx::mbar_init(b_peer + 8 * i, 1);
+            for (int i = lane; i < R; i += 32) ptx::mbar_init(b_peer + 8 * i, Cfg::unified ? 5 : 1);
             for (int i = lane; i < SA; i += 32) ptx::mbar_init(a_peer + 8 * i, 4);
             if (lane == 0) ptx::mbar_init(acc_peer, kEpilogueWarps);
         }
@@ -301,14 +318,14 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     const uint32_t tmem_base = *tmem_holder;   // valid for every warp but the producers, which never use it
 
     if (is_producer) {
-        // ------------------------------------------------------------ producers (one thread each): warps 4 and 5 copy the
+        // ------------------------------------------------------------ producers (a warp each, one elected lane issues): warps 4 and 5 copy the
         // weight segments of the tile's first / second 64-row block, the last warp the activations (one 3-D TMA box per
         // stage).  Weights declared static are requested before griddepcontrol.wait, i.e. while the previous kernel
         // of the stream may still be running; everything else waits for it.
-        if (lane == 0) {
+        {
             const bool acts = warp == kActProducerWarp;
             const uint32_t half = acts ? 0u : (uint32_t)(warp - kProducerWarp);
-            if (warp == kProducerWarp) PROF_STAMP(13);
+            if (warp == kProducerWarp && lane == 0) PROF_STAMP(13);
             const uint64_t pol = acts ? ptx::policy_evict_last() : ptx::policy_evict_first();
             const uint64_t kblocks = plan.kblocks;
             const uint8_t* reg1 = p.region[0];
@@ -333,35 +350,40 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 const int32_t n0 = (int32_t)((seg.tile - p_tile * plan.n_tiles) * N_TILE + half_id * Cfg::n_local);
                 const uint32_t nstages = (seg.nkb + KS - 1) / KS;
                 uint32_t sidx = plan_first_stage(cta, nstages);   // stage of the segment's K range handled next
-                if (warp == kProducerWarp && issued == 0) PROF_STAMP(14);
+                if (warp == kProducerWarp && lane == 0 && issued == 0) PROF_STAMP(14);
                 for (uint32_t i = 0; i < nstages; i++) {
                     const uint32_t kb_off = sidx * KS;
                     const uint32_t cnt = seg.nkb - kb_off < (uint32_t)KS ? seg.nkb - kb_off : (uint32_t)KS;
                     sidx = sidx + 1 == nstages ? 0u : sidx + 1;
-                    if (!PROF_WAIT(0, ptx::mbar_wait(my_empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, Cfg::poll_producer))) { ok = false; break; }
+                    if (!PROF_WAIT(0, ptx::mbar_wait_warp(my_empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, Cfg::poll_producer))) { ok = false; break; }
                     PROF_COUNT(6)
+                    PROF_TRACE(acts ? 0 : 8 + 2 * half, issued);
                     if (!waited) {
                         asm volatile("griddepcontrol.wait;" ::: "memory");   // first read of memory the previous kernel may write
                         waited = true;
                     }
-                    if (warp == kProducerWarp && issued == 0) PROF_STAMP(15);
+                    if (warp == kProducerWarp && lane == 0 && issued == 0) PROF_STAMP(15);
                     PROF_BEGIN(t_issue)
                     const uint32_t bar = my_full + 8 * pos.idx;
                     const uint32_t dst = ring + pos.idx * Cfg::stage_bytes;
-                    if (acts) {
-                        // always KS blocks: blocks past the end of K are zero-filled by the copy
-                        ptx::mbar_arrive_expect_tx(bar, KS * Cfg::b_block);
-                        ptx::tma_load_3d(dst, &act_map, 0, n0, (int32_t)(seg.kb_begin + kb_off), bar, pol);
-                    } else {
-                        ptx::mbar_arrive_expect_tx(bar, cnt * (Raw::bytes128 / 2));
-                        const uint64_t b0 = blk0 + kb_off;
-                        if (Raw::seg1) ptx::bulk_g2s(dst + Cfg::off1 + half * KS * Raw::seg1, reg1 + b0 * Raw::seg1, cnt * Raw::seg1, bar, pol);
-                        if (Raw::seg2) ptx::bulk_g2s(dst + Cfg::off2 + half * KS * Raw::seg2, reg2 + b0 * Raw::seg2, cnt * Raw::seg2, bar, pol);
-                        if (Raw::seg4) ptx::bulk_g2s(dst + Cfg::off4 + half * KS * Raw::seg4, reg4 + b0 * Raw::seg4, cnt * Raw::seg4, bar, pol);
+                    const uint64_t b0 = blk0 + kb_off;
+                    if (ptx::elect_one()) {
+                        if (acts) {
+                            // always KS blocks: blocks past the end of K are zero-filled by the copy
+                            ptx::mbar_arrive_expect_tx(bar, KS * Cfg::b_block);
+                            ptx::tma_load_3d(dst, &act_map, 0, n0, (int32_t)(seg.kb_begin + kb_off), bar, pol);
+                        } else {
+                            ptx::mbar_arrive_expect_tx(bar, cnt * (Raw::bytes128 / 2));
+                            if (Raw::seg1) ptx::bulk_g2s(dst + Cfg::off1 + half * KS * Raw::seg1, reg1 + b0 * Raw::seg1, cnt * Raw::seg1, bar, pol);
+                            if (Raw::seg2) ptx::bulk_g2s(dst + Cfg::off2 + half * KS * Raw::seg2, reg2 + b0 * Raw::seg2, cnt * Raw::seg2, bar, pol);
+                            if (Raw::seg4) ptx::bulk_g2s(dst + Cfg::off4 + half * KS * Raw::seg4, reg4 + b0 * Raw::seg4, cnt * Raw::seg4, bar, pol);
+                        }
                     }
+                    __syncwarp();
                     PROF_END(3, t_issue)
+                    PROF_TRACE(acts ? 1 : 9 + 2 * half, issued);
                     pos.advance(1);
-                    if (warp == kProducerWarp) { if (issued == 0) PROF_STAMP(2); PROF_STAMP(3); }
+                    if (warp == kProducerWarp && lane == 0) { if (issued == 0) PROF_STAMP(2); PROF_STAMP(3); }
                     issued++;
                 }
             }
@@ -369,7 +391,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
                 const uint32_t first = issued > (uint32_t)R ? issued - R : 0u;
                 for (uint32_t t = first; t < issued; t++)
-                    ptx::mbar_wait(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, Cfg::poll_producer, 50000000ull);
+                    ptx::mbar_wait_warp(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, Cfg::poll_producer, 50000000ull);
             }
         }
         __syncwarp();
@@ -395,11 +417,11 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         plan_start(plan, cta, &iter);
         while (ok && plan_next(plan, cta, &iter, &seg)) {
             const uint32_t nstages = (seg.nkb + KS - 1) / KS;
-            if (me < (uint32_t)NI && lane == 0) {
+            if (me < (uint32_t)NI) {   // the whole warp, converged; one elected lane issues
                 if (!relay) {
-                    if (!PROF_WAIT(2, ptx::mbar_wait(acc_empty, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty))) ok = false;
+                    if (!PROF_WAIT(2, ptx::mbar_wait_warp(acc_empty, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty))) ok = false;
                     if constexpr (PAIR)
-                        if (ok && !ptx::mbar_wait(acc_peer, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty)) ok = false;
+                        if (ok && !ptx::mbar_wait_warp(acc_peer, (nseg & 1u) ^ 1u, abort_word, kErrAccEmpty)) ok = false;
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + Cfg::acc_col0 + me * Cfg::acc_stride;
@@ -418,23 +440,27 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     while (sidx >= nstages) sidx -= nstages;
                     const uint32_t cnt = seg.nkb - sidx * KS < (uint32_t)KS ? seg.nkb - sidx * KS : (uint32_t)KS;
                     sidx += IST;
-                    if (!PROF_WAIT(1, ptx::mbar_wait(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                    if (!PROF_WAIT(1, ptx::mbar_wait_warp(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
+                    PROF_TRACE(2, j0 + t);
                     if constexpr (PAIR) {
                         if (relay) {
-                            ptx::mbar_arrive_remote(ptx::mapa(b_peer + 8 * rp.idx, 0u));
+                            ptx::mbar_arrive_remote_elected(ptx::mapa(b_peer + 8 * rp.idx, 0u));
                             rp.advance(IST);
                             continue;
                         }
-                        if (!PROF_WAIT(2, ptx::mbar_wait(b_peer + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
+                        if (!PROF_WAIT(2, ptx::mbar_wait_warp(b_peer + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     }
                     const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::stage_bytes >> 4));
 #pragma unroll
                     for (uint32_t sub = sub0; sub < PPS; sub += (uint32_t)NI) {
-                        if (!PROF_WAIT(0, ptx::mbar_wait(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull, Cfg::poll_issuer))) { ok = false; break; }
-                        if constexpr (PAIR)
-                            if (!PROF_WAIT(4, ptx::mbar_wait(a_peer + 8 * ap.idx, ap.lap, abort_word, kErrAFull, Cfg::poll_issuer))) { ok = false; break; }
-                        if (me == 0 && nseg == 0 && t == 0) PROF_STAMP(5);
+                        if constexpr (!Cfg::unified) {   // unified: the stage's barrier has covered the slot too
+                            if (!PROF_WAIT(0, ptx::mbar_wait_warp(a_full + 8 * ap.idx, ap.lap, abort_word, kErrAFull, Cfg::poll_issuer))) { ok = false; break; }
+                            if constexpr (PAIR)
+                                if (!PROF_WAIT(4, ptx::mbar_wait_warp(a_peer + 8 * ap.idx, ap.lap, abort_word, kErrAFull, Cfg::poll_issuer))) { ok = false; break; }
+                        }
+                        if (me == 0 && lane == 0 && nseg == 0 && t == 0) PROF_STAMP(5);
+                        PROF_TRACE(3, j0 + t);
                         PROF_BEGIN(t_issue)
                         ptx::tc_fence_after_sync();
                         const uint32_t a_tmem = tmem_base + ap.idx * Cfg::slot_cols;
@@ -445,33 +471,34 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
 #pragma unroll
                                 for (uint32_t kk = 0; kk < 4; kk++) {   // four K=16 steps; B advances 32 bytes inside the swizzle row
                                     if constexpr (PAIR)
-                                        ptx::mma_f16_ts_pair(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
-                                                             b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
+                                        ptx::mma_f16_ts_pair_elect(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
+                                                                   b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
                                     else
-                                        ptx::mma_f16_ts(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
-                                                        b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
+                                        ptx::mma_f16_ts_elect(d_tmem, a_tmem + b * kAColsPerKBlock + kk * 8,
+                                                              b_desc + kbi * (Cfg::b_block >> 4) + kk * 2, idesc, accumulate);
                                     accumulate = 1u;
                                 }
                             }
                         }
                         PROF_END(3, t_issue)
                         PROF_BEGIN(t_commit)
-                        if constexpr (PAIR) ptx::tc_commit_pair(a_empty + 8 * ap.idx);
-                        else ptx::tc_commit(a_empty + 8 * ap.idx);
+                        if constexpr (PAIR) ptx::tc_commit_pair_elect(a_empty + 8 * ap.idx);
+                        else ptx::tc_commit_elect(a_empty + 8 * ap.idx);
                         PROF_END(4, t_commit)
+                        PROF_TRACE(4, j0 + t);
                         ap.advance(NI);
                     }
                     if (!ok) break;
                     if (!Cfg::unified) {
-                        if constexpr (PAIR) ptx::tc_commit_pair(b_empty + 8 * rp.idx);
-                        else ptx::tc_commit(b_empty + 8 * rp.idx);
+                        if constexpr (PAIR) ptx::tc_commit_pair_elect(b_empty + 8 * rp.idx);
+                        else ptx::tc_commit_elect(b_empty + 8 * rp.idx);
                     }
-                    if (me == 0) PROF_STAMP(6);
+                    if (me == 0 && lane == 0) PROF_STAMP(6);
                     rp.advance(IST);
                 }
                 if (ok && !relay) {   // arrives once this issuer's MMAs (if any) are done
-                    if constexpr (PAIR) ptx::tc_commit_pair(acc_full);
-                    else ptx::tc_commit(acc_full);
+                    if constexpr (PAIR) ptx::tc_commit_pair_elect(acc_full);
+                    else ptx::tc_commit_elect(acc_full);
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -641,6 +668,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 if (!PROF_WAIT(0, ptx::mbar_wait_warp(w_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull, Cfg::poll_unpack))) { ok = false; break; }
                 if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == cls) PROF_STAMP(4);
                 PROF_COUNT(6)
+                if (q == 0) PROF_TRACE(5, j0 + t);
                 const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
                 load_words(raw, 0);
                 const uint32_t a_addr = a_lane + slot * Cfg::slot_cols;
@@ -668,13 +696,18 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     if (b == 0) {
                         if (!PROF_WAIT(2, ptx::mbar_wait_warp(a_empty + 8 * slot, slot_lap ^ 1u, abort_word, kErrAEmpty, Cfg::poll_unpack))) { ok = false; break; }
                         ptx::tc_fence_after_sync();
+                        if (q == 0) PROF_TRACE(6, j0 + t);
                     }
                     ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock, v[0]);
                     ptx::tmem_st_16x128b_x8(a_addr + b * kAColsPerKBlock + (16u << 16), v[1]);
                 }
                 if (!ok) break;
-                pending_bar = (PAIR && half_id != 0u) ? ptx::mapa(a_peer + 8 * slot, 0u) : a_full + 8 * slot;
+                {
+                    const uint32_t mine = Cfg::unified ? b_full : a_full, peers = Cfg::unified ? b_peer : a_peer;
+                    pending_bar = (PAIR && half_id != 0u) ? ptx::mapa(peers + 8 * slot, 0u) : mine + 8 * slot;
+                }
                 hand_over();
+                if (q == 0) PROF_TRACE(7, j0 + t);
                 slot += kDequantGroups;
                 if (slot >= (uint32_t)SA) { slot -= SA; slot_lap ^= 1u; }
                 rp.advance(ST);
@@ -990,6 +1023,11 @@ cudaError_t launch_by_n(int n_tile, bool pair, cudaStream_t stream, const CUtens
 
 }  // namespace
 
+#ifdef FPX_TRACE
+extern "C" int fp6b200_debug_read_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_trace, sizeof(g_trace));
+}
+#endif
 #ifdef FPX_PROFILE
 extern "C" int fp6b200_debug_read_profile(unsigned long long* host_out) {
     return cudaMemcpyFromSymbol(host_out, g_prof, sizeof(g_prof));

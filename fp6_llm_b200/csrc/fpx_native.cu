@@ -128,7 +128,9 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_dyn + S * Cfg::stage_bytes + 8 * Cfg::num_barriers);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
-    const int warp = threadIdx.x >> 5;
+    // through a shuffle, so that the compiler knows the index to be the same in every lane: the copy and MMA roles are
+    // executed by whole warps with one elected lane issuing, which keeps their addresses and descriptors warp-uniform
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const uint32_t cta = blockIdx.x;
     const WorkPlan& plan = p.plan;
@@ -161,11 +163,11 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     const uint32_t tmem_base = *tmem_holder;
 
     if (warp < 2) {
-        // ------------------------------------------------------------ copy producers (one thread each)
+        // ------------------------------------------------------------ copy producers (a warp each, one elected lane issues)
         // Warp 0: weight tiles; weights declared static are requested before griddepcontrol.wait, i.e. while the
         // previous kernel of the stream may still be running.  Warp 1: the activation planes, which the split
         // kernel just before this one writes, always after the wait.
-        if (lane == 0) {
+        {
             const bool acts = warp == 1;
             const uint64_t pol = acts ? ptx::policy_evict_last() : ptx::policy_evict_first();
             bool waited = !acts && p.weights_static != 0;
@@ -181,21 +183,25 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 for (uint32_t i = 0; i < seg.nkb; i++) {
                     const uint32_t k_tile = seg.kb_begin + kt;
                     kt = kt + 1 == seg.nkb ? 0u : kt + 1;
-                    if (!ptx::mbar_wait(empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, 100)) { ok = false; break; }
+                    if (!ptx::mbar_wait_warp(empty + 8 * pos.idx, pos.lap ^ 1u, abort_word, kErrStageEmpty, 100)) { ok = false; break; }
                     if (!waited) {
                         asm volatile("griddepcontrol.wait;" ::: "memory");
                         waited = true;
                     }
                     const uint32_t bar = full + 8 * pos.idx;
                     const uint32_t dst = ring + pos.idx * Cfg::stage_bytes;
-                    if (acts) {
-                        ptx::mbar_arrive_expect_tx(bar, Cfg::b_bytes);
-                        ptx::tma_load_2d(dst + kNatTileSmem, &x_map, (int32_t)(k_tile * kNatTileK), 0, bar, pol);
-                    } else {
-                        // the transaction count of a 6-bit copy is the bytes read from global memory
-                        ptx::mbar_arrive_expect_tx(bar, (uint32_t)kNatTileBytes);
-                        ptx::tma_load_2d(dst, &w_map, 0, (int32_t)((seg.tile * p.ktiles + k_tile) * kNatTileM), bar, pol);
+                    const int32_t w_row = (int32_t)((seg.tile * p.ktiles + k_tile) * kNatTileM);
+                    if (ptx::elect_one()) {
+                        if (acts) {
+                            ptx::mbar_arrive_expect_tx(bar, Cfg::b_bytes);
+                            ptx::tma_load_2d(dst + kNatTileSmem, &x_map, (int32_t)(k_tile * kNatTileK), 0, bar, pol);
+                        } else {
+                            // the transaction count of a 6-bit copy is the bytes read from global memory
+                            ptx::mbar_arrive_expect_tx(bar, (uint32_t)kNatTileBytes);
+                            ptx::tma_load_2d(dst, &w_map, 0, w_row, bar, pol);
+                        }
                     }
+                    __syncwarp();
                     pos.advance(1);
                     issued++;
                 }
@@ -203,14 +209,14 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
                 const uint32_t first = issued > (uint32_t)S ? issued - S : 0u;
                 for (uint32_t t = first; t < issued; t++)
-                    ptx::mbar_wait(full + 8 * (t % S), (t / S) & 1u, abort_word, kErrStageFull, 100, 50000000ull);
+                    ptx::mbar_wait_warp(full + 8 * (t % S), (t / S) & 1u, abort_word, kErrStageFull, 100, 50000000ull);
             }
         }
         __syncwarp();
     } else if (warp < kNatFirstEpilogue) {
         // ------------------------------------------------------------ MMA issue
         const uint32_t me = (uint32_t)(warp - kNatFirstIssuer);
-        if (me < (uint32_t)NI && lane == 0) {
+        if (me < (uint32_t)NI) {   // the whole warp, converged
             const uint32_t idesc = ptx::idesc_f8f6f4_f32(p.a_format, ptx::kFmtE5M2, kNatTileM, N_TILE);
             const uint64_t desc0 = ptx::smem_desc_k_sw128(ring);
             uint32_t j0 = 0, nseg = 0;   // stages before this segment, segments so far
@@ -220,7 +226,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             plan_start(plan, cta, &iter);
             while (ok && plan_next(plan, cta, &iter, &seg)) {
                 const uint32_t buf = nseg & 1u;
-                if (!ptx::mbar_wait(acc_empty + 8 * buf, ((nseg >> 1) & 1u) ^ 1u, abort_word, kErrAccEmpty)) { ok = false; break; }
+                if (!ptx::mbar_wait_warp(acc_empty + 8 * buf, ((nseg >> 1) & 1u) ^ 1u, abort_word, kErrAccEmpty)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + me * Cfg::acc_stride + buf * N_TILE;
                 uint32_t accumulate = 0u;
@@ -228,20 +234,20 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 ptx::RingPos<S> pos;
                 pos.set(j0 + t);
                 for (; t < seg.nkb; t += NI) {
-                    if (!ptx::mbar_wait(full + 8 * pos.idx, pos.lap, abort_word, kErrStageFull)) { ok = false; break; }
+                    if (!ptx::mbar_wait_warp(full + 8 * pos.idx, pos.lap, abort_word, kErrStageFull)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
                     const uint64_t a_desc = desc0 + (uint64_t)(pos.idx * (Cfg::stage_bytes >> 4));
                     const uint64_t b_desc = a_desc + (kNatTileSmem >> 4);
 #pragma unroll
                     for (uint32_t kk = 0; kk < 4; kk++) {   // four K = 32 steps: 32 bytes further inside the swizzle row
-                        ptx::mma_f8f6f4_ss(d_tmem, a_desc + kk * 2, b_desc + kk * 2, idesc, accumulate);
+                        ptx::mma_f8f6f4_ss_elect(d_tmem, a_desc + kk * 2, b_desc + kk * 2, idesc, accumulate);
                         accumulate = 1u;
                     }
-                    ptx::tc_commit(empty + 8 * pos.idx);
+                    ptx::tc_commit_elect(empty + 8 * pos.idx);
                     pos.advance(NI);
                 }
                 if (!ok) break;
-                ptx::tc_commit(acc_full + 8 * buf);   // arrives once this issuer's MMAs (if any) are done
+                ptx::tc_commit_elect(acc_full + 8 * buf);   // arrives once this issuer's MMAs (if any) are done
                 j0 += seg.nkb;
                 nseg++;
             }
