@@ -120,11 +120,18 @@ struct Config {
     // tensor-memory columns the widest tile leaves free pay for.
     static constexpr int stages = PAIR ? 8 : (ks == 4 ? (N_TILE <= 16 ? 6 : 4) : 4);
     static constexpr int a_slots = PAIR ? 8 : 4;   // one or two slots per unpack group: 64 columns of fp16 weights each, 32 for the widest tile
+    // The activation blocks may have a ring of their own, deeper than the weights' (b_stages > stages).  Measured on the
+    // widest tile (32 KB blocks, 57344 x 8192 at 1024 tokens): six blocks in flight instead of four change nothing
+    // (0.713 against 0.721 ms) - a block then lands 2.4 us after its copy is requested instead of 1.3 us, i.e. the copies
+    // arrive at a fixed ~70 GB/s per SM however many are in flight, with or without the MMAs, the unpack warps and the
+    // weight copies beside them (a loop of nothing but such copies reaches 180 GB/s per SM).  So the rings stay one.
+    static constexpr int b_stages = stages;
+    static constexpr bool split_rings = b_stages != stages;
     static constexpr int pos_per_stage = ks / kpw;
     // When every stage is one position and the two rings are equally deep, slot and stage coincide and ONE commit of the
     // issuing warp frees both the tensor-memory slot and the stage's activations (measured 6 % faster on the widest
     // tile than two commits; the weights of a stage are still handed back by the unpack warps as soon as they are read).
-    static constexpr bool unified = (ks == kpw) && (a_slots == stages);
+    static constexpr bool unified = (ks == kpw) && (a_slots == stages) && !split_rings;
     // One thread can issue an MMA only every ~45-130 cycles and the narrow MMAs occupy the tensor pipe for ~40 only,
     // so narrow tiles are issued by several warps, each into an accumulator of its own (the epilogue adds them up).
     static constexpr int issuers = N_TILE <= 64 ? 4 : (N_TILE <= 128 ? 2 : 1);
@@ -148,19 +155,25 @@ struct Config {
     // the unpack warps of a wide tile are ahead of the tensor pipe most of the time: every poll they save is power for it
     static constexpr uint32_t poll_unpack = N_TILE <= 128 ? ptx::kPollFast : kPollUnpackWide;
     static constexpr uint32_t b_block = (uint32_t)n_local * 128u;
-    static constexpr uint32_t w_off = ks * b_block;
+    // shared memory: either `stages` stages of [activation blocks | weight segments], or (split_rings) the ring of
+    // activation blocks followed by the ring of weight segments
+    static constexpr uint32_t w_stage = ks * Raw::bytes128;
+    static constexpr uint32_t b_stride = split_rings ? ks * b_block : ks * b_block + w_stage;   // from one stage's activations to the next
+    static constexpr uint32_t w_stride = split_rings ? w_stage : ks * b_block + w_stage;        // from one stage's weights to the next
+    static constexpr uint32_t w_off = split_rings ? b_stages * ks * b_block : ks * b_block;    // the weights of stage 0
     static constexpr uint32_t off1 = w_off;
     static constexpr uint32_t off2 = off1 + 2u * ks * Raw::seg1;
     static constexpr uint32_t off4 = off2 + 2u * ks * Raw::seg2;
-    static constexpr uint32_t stage_bytes = ks * (b_block + Raw::bytes128);
+    static constexpr uint32_t ring_bytes = b_stages * ks * b_block + stages * w_stage;
     static constexpr uint32_t slot_cols = kpw * kAColsPerKBlock;
     static constexpr uint32_t acc_col0 = a_slots * slot_cols;
     static constexpr uint32_t acc_stride = N_TILE < 32 ? 32u : (uint32_t)N_TILE;
-    static_assert(stage_bytes % 1024 == 0, "activation blocks must stay 1024-byte aligned");
+    static_assert(b_stride % 1024 == 0, "activation blocks must stay 1024-byte aligned");
+    static_assert(b_stages % issuer_step == 0, "an issuing warp must meet an activation slot again on the slot's next use");
     static_assert(acc_col0 + issuers * acc_stride <= kTmemCols, "tensor memory budget");
     // + for a pair: the peer's "activations landed" per stage, "slot stored" per slot and "accumulator read" words
-    static constexpr int num_barriers = 4 * stages + 2 * a_slots + 2 + (PAIR ? stages + a_slots + 1 : 0);
-    static constexpr uint32_t used_bytes = stages * stage_bytes + num_barriers * 8u + 32u;
+    static constexpr int num_barriers = 2 * stages + 2 * b_stages + 2 * a_slots + 2 + (PAIR ? stages + a_slots + 1 : 0);
+    static constexpr uint32_t used_bytes = ring_bytes + num_barriers * 8u + 32u;
     static constexpr uint32_t smem_bytes = used_bytes > 116u * 1024u ? used_bytes : 116u * 1024u;   // never two CTAs per SM
     static_assert(2u * smem_bytes > 228u * 1024u, "two CTAs must never share an SM: each takes all of tensor memory");
     static_assert(!PAIR || (issuers == 1 && N_TILE % 32 == 0), "a pair has one issuing thread");
@@ -231,6 +244,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     using Raw = typename Cfg::Raw;
     constexpr int KS = Cfg::ks;
     constexpr int R = Cfg::stages;
+    constexpr int RB = Cfg::b_stages;
     constexpr int SA = Cfg::a_slots;
     constexpr int NI = Cfg::issuers;
 
@@ -239,11 +253,11 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     // everything in shared memory is addressed by 32-bit shared-space addresses
     const uint32_t ring = ptx::smem_u32(smem_dyn);
-    const uint32_t w_full = ring + R * Cfg::stage_bytes; // barrier arrays, 8 bytes per barrier: the stage's weights have landed
+    const uint32_t w_full = ring + Cfg::ring_bytes;      // barrier arrays, 8 bytes per barrier: the stage's weights have landed
     const uint32_t b_full = w_full + 8 * R;              // the stage's activations have landed
-    const uint32_t w_empty = b_full + 8 * R;             // the unpack warps have read the weights of the stage
+    const uint32_t w_empty = b_full + 8 * RB;            // the unpack warps have read the weights of the stage
     const uint32_t b_empty = w_empty + 8 * R;            // the MMAs that read the activations of the stage are done
-    const uint32_t a_full = b_empty + 8 * R;             // per tensor-memory slot: the K block's fp16 weights are stored
+    const uint32_t a_full = b_empty + 8 * RB;            // per tensor-memory slot: the K block's fp16 weights are stored
     const uint32_t a_empty = a_full + 8 * SA;            // per slot: the MMAs that read it are done
     const uint32_t acc_full = a_empty + 8 * SA;
     const uint32_t acc_empty = acc_full + 8;
@@ -252,7 +266,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     const uint32_t b_peer = acc_empty + 8;
     const uint32_t a_peer = b_peer + 8 * R;
     const uint32_t acc_peer = a_peer + 8 * SA;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_dyn + R * Cfg::stage_bytes + 8 * Cfg::num_barriers);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem_dyn + Cfg::ring_bytes + 8 * Cfg::num_barriers);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     // the warp's index, taken through a shuffle so that the compiler knows it to be the same in every lane: the roles that
@@ -277,10 +291,12 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     if (warp == kProducerWarp) {   // one barrier per lane and round
         for (int i = lane; i < R; i += 32) {
             ptx::mbar_init(w_full + 8 * i, kProducerWarps);
+            ptx::mbar_init(w_empty + 8 * i, Cfg::readers);
+        }
+        for (int i = lane; i < RB; i += 32) {
             // unified: "activations landed" and "slot stored" share the barrier (the copy's arrival + four unpack warps),
             // so that the issuing warp waits once per position; the second CTA of a pair reports both to the first
             ptx::mbar_init(b_full + 8 * i, Cfg::unified && half_id == 0u ? 5 : 1);
-            ptx::mbar_init(w_empty + 8 * i, Cfg::readers);
             ptx::mbar_init(b_empty + 8 * i, Cfg::stage_issuers);
         }
         for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, 4); ptx::mbar_init(a_empty + 8 * i, 1); }
@@ -334,8 +350,10 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             const uint32_t my_full = acts ? b_full : w_full;
             const uint32_t my_empty = acts ? (Cfg::unified ? a_empty : b_empty) : w_empty;
             bool waited = !acts && p.weights_static != 0;   // nothing to wait for before static weights are read
-            ptx::RingPos<R> pos;
-            pos.set(0);
+            // the ring this warp fills: activation blocks or weight segments (two rings of different depth for the widest tile)
+            const uint32_t ring_n = acts ? (uint32_t)RB : (uint32_t)R;
+            const uint32_t ring_stride = acts ? Cfg::b_stride : Cfg::w_stride;
+            struct { uint32_t idx, lap; } pos = {0u, 0u};
             uint32_t issued = 0;
             bool ok = true;
             SegmentIter iter;
@@ -365,7 +383,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     if (warp == kProducerWarp && lane == 0 && issued == 0) PROF_STAMP(15);
                     PROF_BEGIN(t_issue)
                     const uint32_t bar = my_full + 8 * pos.idx;
-                    const uint32_t dst = ring + pos.idx * Cfg::stage_bytes;
+                    const uint32_t dst = ring + pos.idx * ring_stride;
                     const uint64_t b0 = blk0 + kb_off;
                     if (ptx::elect_one()) {
                         if (acts) {
@@ -382,16 +400,16 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     __syncwarp();
                     PROF_END(3, t_issue)
                     PROF_TRACE(acts ? 1 : 9 + 2 * half, issued);
-                    pos.advance(1);
+                    if (++pos.idx == ring_n) { pos.idx = 0; pos.lap ^= 1u; }
                     if (warp == kProducerWarp && lane == 0) { if (issued == 0) PROF_STAMP(2); PROF_STAMP(3); }
                     issued++;
                 }
             }
             PROF_FLUSH();
             if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
-                const uint32_t first = issued > (uint32_t)R ? issued - R : 0u;
+                const uint32_t first = issued > ring_n ? issued - ring_n : 0u;
                 for (uint32_t t = first; t < issued; t++)
-                    ptx::mbar_wait_warp(my_full + 8 * (t % R), (t / R) & 1u, abort_word, kErrStageFull, Cfg::poll_producer, 50000000ull);
+                    ptx::mbar_wait_warp(my_full + 8 * (t % ring_n), (t / ring_n) & 1u, abort_word, kErrStageFull, Cfg::poll_producer, 50000000ull);
             }
         }
         __syncwarp();
@@ -430,7 +448,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 const uint32_t sub0 = me % PPS;                                  // first position of mine inside a stage
                 const uint32_t cls_i = (me / PPS) % IST;
                 uint32_t t = (cls_i + IST - (j0 % IST)) % IST;                    // my first stage of the segment
-                ptx::RingPos<R> rp;
+                ptx::RingPos<RB> rp;
                 ptx::RingPos<SA> ap;
                 rp.set(j0 + t);
                 ap.set((j0 + t) * PPS + sub0);
@@ -451,7 +469,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                         }
                         if (!PROF_WAIT(2, ptx::mbar_wait_warp(b_peer + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     }
-                    const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::stage_bytes >> 4));
+                    const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::b_stride >> 4));
 #pragma unroll
                     for (uint32_t sub = sub0; sub < PPS; sub += (uint32_t)NI) {
                         if constexpr (!Cfg::unified) {   // unified: the stage's barrier has covered the slot too
@@ -669,7 +687,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 if (warp == kFirstDequantWarp && lane == 0 && j0 == 0 && t == cls) PROF_STAMP(4);
                 PROF_COUNT(6)
                 if (q == 0) PROF_TRACE(5, j0 + t);
-                const uint32_t raw = lane_base + rp.idx * Cfg::stage_bytes;   // shared-space byte address of this lane's words
+                const uint32_t raw = lane_base + rp.idx * Cfg::w_stride;   // shared-space byte address of this lane's words
                 load_words(raw, 0);
                 const uint32_t a_addr = a_lane + slot * Cfg::slot_cols;
 #pragma unroll
