@@ -23,7 +23,10 @@
 //               the position's slot, stores, and hands the slot to the issuing warp;
 //   warps 0-3   issue tcgen05.mma.kind::f16 with A from tensor memory and B from shared memory, accumulating
 //               fp32 in tensor memory; issuer i takes the positions i, i + issuers, ... (up to four issuers, each with
-//               its own accumulator, because one thread cannot issue MMAs fast enough for narrow tiles).  At the end
+//               its own accumulator).  An issuer is a WHOLE warp, converged, with one elected lane issuing: the warp
+//               index comes through a shuffle, so addresses and descriptors stay warp-uniform, and a round of four
+//               MMAs and a commit costs ~64 cycles where a branch taken by one lane alone pays ~230, plus ~200 for
+//               every barrier wait whose result it consumes (the copy producers issue the same way).  At the end
 //               of a segment the same four warps (one per tensor-memory lane quadrant) read the accumulators
 //               with tcgen05.ld, add them, multiply by 2^bias * scale[row] in fp32 (the per-row scale is
 //               applied here, once per output, not once per weight), add the bias, apply the fused activation and
@@ -58,8 +61,8 @@ constexpr int gemm_ks(int n_tile) { return n_tile <= 64 ? 4 : (n_tile <= 128 ? 2
 
 constexpr int kTileM = 128;
 constexpr int kAColsPerKBlock = 32;      // 64 fp16 along K per tensor-memory lane
-constexpr int kMaxIssuers = 4;           // warps 0..3: MMA issuers (lane 0 of each) and, one per lane quadrant, the epilogue
-constexpr int kProducerWarp = 4;         // warps 4,5: one thread each; a thread can start a bulk copy only every ~100 cycles
+constexpr int kMaxIssuers = 4;           // warps 0..3: MMA issuers (whole warps, one elected lane) and, one per lane quadrant, the epilogue
+constexpr int kProducerWarp = 4;         // warps 4,5: the weights' copy producers (whole warps, one elected lane)
 constexpr int kProducerWarps = 2;
 constexpr int kFirstDequantWarp = kProducerWarp + kProducerWarps;
 constexpr int kDequantGroups = 4;        // a group = 4 consecutive warps, one per tensor-memory lane quadrant
@@ -102,12 +105,12 @@ struct RawBlock {
 // own tensor memory and loads HALF of the activation tile (N_TILE / 2 token rows); the first CTA issues
 // tcgen05.mma.cta_group::2 for both (M = 256), whose B operand is read from both shared memories.  The activation tile,
 // which a wide tile otherwise re-reads from L2 for every 128 output channels, is read once per 256.
-// Correct (tests) but NOT the default: on the 57344 x 8192 layer at 1024 tokens it takes 1.53 ms against 0.92 ms, with 4 as
+// Correct (tests) but NOT the default: on the 57344 x 8192 layer at 1024 tokens it takes 1.37 ms against 0.72 ms, with 4 as
 // with 8 ring slots.  Measured: the pair's MMAs run at the full rate in isolation (128 cycles per M256 x N256 x K16, with
 // multicast commits and concurrent tensor-memory stores), the L2 -> SM traffic does fall (7.5 -> 5.2 GB), and every role
-// waits for the activation copies: a CTA's 16 KB boxes land one per ~1 us (16 GB/s per SM) where the single CTA's 32 KB
-// boxes land one per 0.6 us, whether the activations are read in the caller's layout or re-laid K block by K block.
-// FP6B200_OPTION_PAIR_TILES turns it on.
+// waits for the activation copies: a CTA's own 16 KB boxes land ~7 us after they are requested with eight in flight
+// (19 GB/s per SM) where the single CTA's 32 KB boxes land after ~1.2 us with four, whether the activations are read in
+// the caller's layout or re-laid K block by K block.  FP6B200_OPTION_PAIR_TILES turns it on.
 template <int BW, int N_TILE, bool PAIR = false>
 struct Config {
     using Raw = RawBlock<BW>;
@@ -132,8 +135,9 @@ struct Config {
     // issuing warp frees both the tensor-memory slot and the stage's activations (measured 6 % faster on the widest
     // tile than two commits; the weights of a stage are still handed back by the unpack warps as soon as they are read).
     static constexpr bool unified = (ks == kpw) && (a_slots == stages) && !split_rings;
-    // One thread can issue an MMA only every ~45-130 cycles and the narrow MMAs occupy the tensor pipe for ~40 only,
-    // so narrow tiles are issued by several warps, each into an accumulator of its own (the epilogue adds them up).
+    // A warp needs ~60 cycles for a barrier wait and ~64 for four MMAs and a commit, and the narrow MMAs occupy the
+    // tensor pipe for ~40 cycles only, so narrow tiles are issued by several warps, each into an accumulator of its own
+    // (the epilogue adds them up).
     static constexpr int issuers = N_TILE <= 64 ? 4 : (N_TILE <= 128 ? 2 : 1);
     static constexpr int stage_step = kDequantGroups / pos_per_stage;   // an unpack group visits every stage_step-th stage
     static constexpr int issuer_step = issuers > pos_per_stage ? issuers / pos_per_stage : 1;   // same for an issuing warp
@@ -415,7 +419,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         __syncwarp();
     } else if (warp < kMaxIssuers) {
         // ------------------------------------------------------------ MMA issue + epilogue
-        // Per segment: lane 0 of the first NI warps issues the MMAs (issuer i takes the K blocks i, i + NI, ... of every
+        // Per segment: the first NI warps issue the MMAs, each converged with one elected lane (issuer i takes the K blocks i, i + NI, ... of every
         // stage, each as soon as its slot of the tensor-memory ring is full, and accumulates them in its own
         // accumulator); then all four warps, one per tensor-memory lane quadrant, read the accumulators, add them and
         // store the tile (lane = output channel, column = token).

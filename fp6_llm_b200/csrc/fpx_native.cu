@@ -22,8 +22,9 @@
 //                (no kernel before the GEMM); for 5..64 tokens split_activations_kernel writes the
 //                planes [4 * tokens][K] beforehand and a tensor copy brings them in;
 //   kernel       persistent, one CTA per SM: warp 0 copies weight tiles, warp 1 the activations, warps 2-5 issue
-//                the MMAs (four K = 32 steps per stage; one thread can issue an MMA only every ~110 cycles and a stage must
-//                not take more than ~550, so up to four warps take the stages in turn, each into its own accumulator),
+//                the MMAs (four K = 32 steps per stage; up to four warps take the stages in turn, each into its own
+//                accumulator; copies and MMAs are issued by whole converged warps with one elected lane, which keeps
+//                addresses and descriptors warp-uniform: ~64 cycles for four MMAs and a commit, ~230 from a lone lane),
 //                warps 6-9 are the epilogue (two accumulator buffers per issuer, so the epilogue of one segment runs
 //                under the main loop of the next), warps 10.. the converters.  Work plan, stream-K partials, fix-up kernel, output targets and
 //                fused epilogues are those of fpx_gemm.cu.
@@ -50,7 +51,7 @@ constexpr int kNatRowBytes = kNatTileK * 6 / 8;        // 96 bytes of HBM per ti
 constexpr int kNatTileBytes = kNatTileM * kNatRowBytes;   // 12 KB of HBM per tile
 constexpr uint32_t kNatTileSmem = kNatTileM * 128;     // 16 KB of shared memory per tile (16 codes -> 16 bytes)
 constexpr int kPieces = 4;
-constexpr int kNatFirstIssuer = 2;             // warps 2..5: MMA issue (lane 0 of the first `issuers` of them)
+constexpr int kNatFirstIssuer = 2;             // warps 2..5: MMA issue (the first `issuers` of them, one elected lane each)
 constexpr int kNatMaxIssuers = 4;
 constexpr int kNatFirstEpilogue = kNatFirstIssuer + kNatMaxIssuers;   // warps 6..9: one per tensor-memory lane quadrant
 constexpr int kNatFirstConverter = kNatFirstEpilogue + 4;   // warps 10..: split the fp16 activations (fused variant only)
