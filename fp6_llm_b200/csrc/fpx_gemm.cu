@@ -371,7 +371,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 // a pair splits the tile's token rows: this CTA copies its half
                 const int32_t n0 = (int32_t)((seg.tile - p_tile * plan.n_tiles) * N_TILE + half_id * Cfg::n_local);
                 const uint32_t nstages = (seg.nkb + KS - 1) / KS;
-                uint32_t sidx = plan_first_stage(cta, nstages);   // stage of the segment's K range handled next
+                uint32_t sidx = plan_first_stage(plan, cta, nstages);   // stage of the segment's K range handled next
                 if (warp == kProducerWarp && lane == 0 && issued == 0) PROF_STAMP(14);
                 for (uint32_t i = 0; i < nstages; i++) {
                     const uint32_t kb_off = sidx * KS;
@@ -456,7 +456,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 ptx::RingPos<SA> ap;
                 rp.set(j0 + t);
                 ap.set((j0 + t) * PPS + sub0);
-                uint32_t sidx = plan_first_stage(cta, nstages) + t;              // stage of the segment's K range handled next
+                uint32_t sidx = plan_first_stage(plan, cta, nstages) + t;              // stage of the segment's K range handled next
                 uint32_t accumulate = 0u;                                        // 0 only for this issuer's first MMA of the segment
                 for (; ok && t < nstages; t += IST) {
                     while (sidx >= nstages) sidx -= nstages;
@@ -530,7 +530,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
             uint32_t has_data = 0;
             {
                 constexpr uint32_t PPS = (uint32_t)Cfg::pos_per_stage, IST = (uint32_t)Cfg::issuer_step;
-                const uint32_t first_stage = plan_first_stage(cta, nstages);
+                const uint32_t first_stage = plan_first_stage(plan, cta, nstages);
 #pragma unroll
                 for (uint32_t i = 0; i < (uint32_t)NI; i++) {
                     const uint32_t t_first = ((i / PPS) % IST + IST - (j0 % IST)) % IST;

@@ -180,7 +180,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             Segment seg;
             plan_start(plan, cta, &iter);
             while (ok && plan_next(plan, cta, &iter, &seg)) {
-                uint32_t kt = plan_first_stage(cta, seg.nkb);
+                uint32_t kt = plan_first_stage(plan, cta, seg.nkb);
                 for (uint32_t i = 0; i < seg.nkb; i++) {
                     const uint32_t k_tile = seg.kb_begin + kt;
                     kt = kt + 1 == seg.nkb ? 0u : kt + 1;
@@ -283,7 +283,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 }
             };
             auto request = [&](uint4 (&dst)[kPerLane]) {                // loads of the cursor's stage
-                uint32_t kt = plan_first_stage(cta, seg.nkb) + in_seg;
+                uint32_t kt = plan_first_stage(plan, cta, seg.nkb) + in_seg;
                 if (kt >= seg.nkb) kt -= seg.nkb;
                 const uint32_t k0 = (seg.kb_begin + kt) * kNatTileK;
 #pragma unroll
