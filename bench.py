@@ -56,7 +56,7 @@ MIN_TIMED_SECONDS = 0.25
 # one layer of the workload (too large to capture whole); recorded when the capture was made, NOT measured in this run.
 RECORDED_TRAFFIC_RATIO = {
     "llama2-70b-fp6": (1.01, "profiler captures of single launches of this workload (gate_up at 1, 16 and 64 tokens: DRAM read + write "
-                             "= 1.012, 1.010 and 0.998 x the launch's algorithmic bytes; summaries under profiles/), scaled to the "
+                             "= 1.010, 1.010 and 0.996 x the launch's algorithmic bytes; summaries under profiles/), scaled to the "
                              "average launch of a step; recorded, not measured in this run"),
 }
 

@@ -51,6 +51,14 @@ constexpr int kNatRowBytes = kNatTileK * 6 / 8;        // 96 bytes of HBM per ti
 constexpr int kNatTileBytes = kNatTileM * kNatRowBytes;   // 12 KB of HBM per tile
 constexpr uint32_t kNatTileSmem = kNatTileM * 128;     // 16 KB of shared memory per tile (16 codes -> 16 bytes)
 constexpr int kPieces = 4;
+// Optional milestones of every CTA (build with -DFPX_PROFILE): global-timer stamps read back with
+// fp6b200_debug_read_native_stamps.
+#ifdef FPX_PROFILE
+__device__ unsigned long long g_nat_stamp[160][8];
+#define NAT_STAMP(slot) do { if (blockIdx.x < 160) g_nat_stamp[blockIdx.x][slot] = ptx::global_timer_ns(); } while (0)
+#else
+#define NAT_STAMP(slot) do { } while (0)
+#endif
 constexpr int kNatFirstIssuer = 2;             // warps 2..5: MMA issue (the first `issuers` of them, one elected lane each)
 constexpr int kNatMaxIssuers = 4;
 constexpr int kNatFirstEpilogue = kNatFirstIssuer + kNatMaxIssuers;   // warps 6..9: one per tensor-memory lane quadrant
@@ -137,6 +145,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     const WorkPlan& plan = p.plan;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the fix-up kernel may become resident
+    if (threadIdx.x == 0) NAT_STAMP(0);   // entry
     if ((ring & 1023u) != 0u) {
         if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrSmemAlign);
         return;
@@ -162,11 +171,15 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    if (threadIdx.x == 0) NAT_STAMP(1);   // set-up done
 
     if (warp < 2) {
         // ------------------------------------------------------------ copy producers (a warp each, one elected lane issues)
         // Warp 0: weight tiles; weights declared static are requested before griddepcontrol.wait, i.e. while the
-        // previous kernel of the stream may still be running.  Warp 1: the activation planes, which the split
+        // previous kernel of the stream may still be running.  (Asking L2 at that point for the 20 tiles that follow the ring's
+        // as well - cp.async.bulk.prefetch.L2, 35 MB over the GPU - measured slower, 12.1 -> 12.5 us on 8192 x 8192 at one
+        // token and 32.8 -> 36.1 us on 8192 x 28672 at 16: the memory system is already busy filling the rings and
+        // finishing the previous layer in that window.)  Warp 1: the activation planes, which the split
         // kernel just before this one writes, always after the wait.
         {
             const bool acts = warp == 1;
@@ -236,6 +249,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 pos.set(j0 + t);
                 for (; t < seg.nkb; t += NI) {
                     if (!ptx::mbar_wait_warp(full + 8 * pos.idx, pos.lap, abort_word, kErrStageFull)) { ok = false; break; }
+                    if (me == 0 && lane == 0 && nseg == 0 && accumulate == 0u) NAT_STAMP(2);   // first stage in place
                     ptx::tc_fence_after_sync();
                     const uint64_t a_desc = desc0 + (uint64_t)(pos.idx * (Cfg::stage_bytes >> 4));
                     const uint64_t b_desc = a_desc + (kNatTileSmem >> 4);
@@ -249,6 +263,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 }
                 if (!ok) break;
                 ptx::tc_commit_elect(acc_full + 8 * buf);   // arrives once this issuer's MMAs (if any) are done
+                if (me == 0 && lane == 0) NAT_STAMP(3);   // last commit of a segment issued
                 j0 += seg.nkb;
                 nseg++;
             }
@@ -473,11 +488,13 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             ptx::tc_fence_before_sync();
             __syncwarp();
             ptx::mbar_arrive_elected(acc_empty + 8 * buf);
+            if (warp == kNatFirstEpilogue && lane == 0) NAT_STAMP(4);   // epilogue of a segment done
             nseg++;
         }
     }
 
     // ------------------------------------------------------------ teardown
+    if (threadIdx.x == 0) NAT_STAMP(5);   // roles done
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (warp == kNatFirstIssuer) {
@@ -490,6 +507,7 @@ fpx_native_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         ptx::tmem_dealloc(tmem_base, Cfg::tmem_cols);
     }
     if (threadIdx.x == 0 && *abort_word != 0) atomicCAS(p.status, 0, *abort_word);
+    if (threadIdx.x == 0) NAT_STAMP(6);   // exit
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -806,3 +824,9 @@ int native_kernel_launches(size_t M, size_t N, size_t K) {
 }
 
 }  // namespace fpx
+
+#ifdef FPX_PROFILE
+extern "C" int fp6b200_debug_read_native_stamps(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, fpx::g_nat_stamp, sizeof(fpx::g_nat_stamp));
+}
+#endif
