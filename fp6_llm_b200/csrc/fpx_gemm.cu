@@ -125,9 +125,9 @@ struct Config {
     static constexpr int a_slots = PAIR ? 8 : 4;   // one or two slots per unpack group: 64 columns of fp16 weights each, 32 for the widest tile
     // The activation blocks may have a ring of their own, deeper than the weights' (b_stages > stages).  Measured on the
     // widest tile (32 KB blocks, 57344 x 8192 at 1024 tokens): six blocks in flight instead of four change nothing
-    // (0.713 against 0.721 ms) - a block then lands 2.4 us after its copy is requested instead of 1.3 us, i.e. the copies
-    // arrive at a fixed ~70 GB/s per SM however many are in flight, with or without the MMAs, the unpack warps and the
-    // weight copies beside them (a loop of nothing but such copies reaches 180 GB/s per SM).  So the rings stay one.
+    // (0.713 against 0.721 ms): the copies are not what the tile waits for.  Per position the MMAs read 32 KB of shared
+    // memory, the copies write 38 KB and the unpack warps read 6 KB: 76 KB at 128 B/clk = 594 cycles for 512 cycles of
+    // tensor work, which is the 84 % tensor-pipe activity the profiler reports.  So the rings stay one.
     static constexpr int b_stages = stages;
     static constexpr bool split_rings = b_stages != stages;
     static constexpr int pos_per_stage = ks / kpw;
