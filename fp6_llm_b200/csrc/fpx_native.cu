@@ -75,7 +75,8 @@ struct NatCfg {
     // g + conv_groups, ... (a stage's conversion is a chain of dependent steps, so several stages must be in work at once;
     // all warps on one stage measured 50 % slower than the separate kernel).  With more tokens the separate kernel
     // measured faster (gate_up 57344 x 8192: 64.9 us against 65.7 us at 8 tokens, 66 us against 72 us at 16), whatever the
-    // number of converter warps.
+    // number of converter warps; measured again with the MMAs issued by elected lanes: equal at 8 tokens (57.5 against
+    // 58.8 us there, 15.3 against 14.9 us on 10240 x 8192), 3-6 % slower at 16.
     static constexpr bool fused = N_TILE <= 16;
     static constexpr int conv_groups = fused ? 4 : 0;
     static constexpr int conv_width = 1;
