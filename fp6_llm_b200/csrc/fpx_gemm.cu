@@ -105,12 +105,10 @@ struct RawBlock {
 // own tensor memory and loads HALF of the activation tile (N_TILE / 2 token rows); the first CTA issues
 // tcgen05.mma.cta_group::2 for both (M = 256), whose B operand is read from both shared memories.  The activation tile,
 // which a wide tile otherwise re-reads from L2 for every 128 output channels, is read once per 256.
-// Correct (tests) but NOT the default: on the 57344 x 8192 layer at 1024 tokens it takes 1.37 ms against 0.72 ms, with 4 as
-// with 8 ring slots.  Measured: the pair's MMAs run at the full rate in isolation (128 cycles per M256 x N256 x K16, with
-// multicast commits and concurrent tensor-memory stores), the L2 -> SM traffic does fall (7.5 -> 5.2 GB), and every role
-// waits for the activation copies: a CTA's own 16 KB boxes land ~7 us after they are requested with eight in flight
-// (19 GB/s per SM) where the single CTA's 32 KB boxes land after ~1.2 us with four, whether the activations are read in
-// the caller's layout or re-laid K block by K block.  FP6B200_OPTION_PAIR_TILES turns it on.
+// Correct (tests) but NOT the default: on the 57344 x 8192 layer at 1024 tokens it takes 0.73 ms against 0.66 ms.
+// Measured: the pair's MMAs run at the full rate in isolation (128 cycles per M256 x N256 x K16, with multicast commits
+// and concurrent tensor-memory stores), the L2 -> SM traffic does fall (7.5 -> 5.2 GB); in the kernel every role waits
+// for completed MMAs, which take ~180 cycles each.  FP6B200_OPTION_PAIR_TILES turns it on.
 template <int BW, int N_TILE, bool PAIR = false>
 struct Config {
     using Raw = RawBlock<BW>;
@@ -265,8 +263,9 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
     const uint32_t a_empty = a_full + 8 * SA;            // per slot: the MMAs that read it are done
     const uint32_t acc_full = a_empty + 8 * SA;
     const uint32_t acc_empty = acc_full + 8;
-    // pair only, used in the first CTA: what the second CTA reports (its half of the stage's activations has landed, its
-    // unpack warps have stored the slot, its epilogue warps have read the accumulator)
+    // pair only, used in the first CTA: what the second CTA reports when slot and stage do not share a barrier (its unpack
+    // warps have stored the slot) and that its epilogue warps have read the accumulator.  In the configuration that exists
+    // (slot = stage) the second CTA's copies and unpack warps arrive on the first CTA's b_full directly and b_peer is unused.
     const uint32_t b_peer = acc_empty + 8;
     const uint32_t a_peer = b_peer + 8 * R;
     const uint32_t acc_peer = a_peer + 8 * SA;
@@ -300,13 +299,12 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         for (int i = lane; i < RB; i += 32) {
             // unified: "activations landed" and "slot stored" share the barrier (the copy's arrival + four unpack warps),
             // so that the issuing warp waits once per position; the second CTA of a pair reports both to the first
-            ptx::mbar_init(b_full + 8 * i, Cfg::unified && half_id == 0u ? 5 : 1);
+            ptx::mbar_init(b_full + 8 * i, Cfg::unified && half_id == 0u ? (PAIR ? 9 : 5) : 1);
             ptx::mbar_init(b_empty + 8 * i, Cfg::stage_issuers);
         }
         for (int i = lane; i < SA; i += 32) { ptx::mbar_init(a_full + 8 * i, 4); ptx::mbar_init(a_empty + 8 * i, 1); }
         if (lane == 0) { ptx::mbar_init(acc_full, NI); ptx::mbar_init(acc_empty, kEpilogueWarps); }
         if constexpr (PAIR) {
-            for (int i = lane; i < R; i += 32) ptx::mbar_init(b_peer + 8 * i, Cfg::unified ? 5 : 1);
             for (int i = lane; i < SA; i += 32) ptx::mbar_init(a_peer + 8 * i, 4);
             if (lane == 0) ptx::mbar_init(acc_peer, kEpilogueWarps);
         }
@@ -390,7 +388,12 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                     const uint32_t dst = ring + pos.idx * ring_stride;
                     const uint64_t b0 = blk0 + kb_off;
                     if (ptx::elect_one()) {
-                        if (acts) {
+                        if (acts && PAIR) {
+                            // both halves of the activation tile are counted on the FIRST CTA's barrier, which expects the
+                            // bytes of both: the issuing warp there waits once, and nothing has to pass the news on
+                            if (half_id == 0u) ptx::mbar_arrive_expect_tx(bar, 2u * KS * Cfg::b_block);
+                            ptx::tma_load_3d_pair(dst, &act_map, 0, n0, (int32_t)(seg.kb_begin + kb_off), ptx::mapa(bar, 0u), pol);
+                        } else if (acts) {
                             // always KS blocks: blocks past the end of K are zero-filled by the copy
                             ptx::mbar_arrive_expect_tx(bar, KS * Cfg::b_block);
                             ptx::tma_load_3d(dst, &act_map, 0, n0, (int32_t)(seg.kb_begin + kb_off), bar, pol);
@@ -410,7 +413,10 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 }
             }
             PROF_FLUSH();
-            if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
+            if (*abort_word != 0 && PAIR && acts && half_id != 0u) {   // this CTA's copies are counted in the other CTA: just give them time
+                const uint64_t t0 = ptx::global_timer_ns();
+                while (ptx::global_timer_ns() - t0 < 1000000ull) { }
+            } else if (*abort_word != 0) {   // gave up somewhere: let the copies in flight land before leaving
                 const uint32_t first = issued > ring_n ? issued - ring_n : 0u;
                 for (uint32_t t = first; t < issued; t++)
                     ptx::mbar_wait_warp(my_full + 8 * (t % ring_n), (t / ring_n) & 1u, abort_word, kErrStageFull, Cfg::poll_producer, 50000000ull);
@@ -424,8 +430,12 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
         // accumulator); then all four warps, one per tensor-memory lane quadrant, read the accumulators, add them and
         // store the tile (lane = output channel, column = token).
         constexpr uint32_t idesc = ptx::idesc_f16_f32(PAIR ? 2 * kTileM : kTileM, N_TILE);
-        // In a pair the first CTA issues for both; the issuing thread of the second only passes on, stage by stage, that
-        // its half of the activations has landed.
+        // In a pair the first CTA issues for both.  The second CTA's issuing warp has nothing to do in the main loop: its
+        // activation copies are counted on the first CTA's barrier (a copy may name a barrier of either CTA of the pair) and
+        // its unpack warps arrive there too.  (An earlier form had this warp wait for its own copies and pass the news on
+        // with a remote arrive: with the .release.cluster arrive that cost ~1300 cycles per stage and bounded the pair at
+        // 1.37 ms on 57344 x 8192 at 1024 tokens; without the relay 0.78 ms, with plain remote arrives 0.73 ms, against
+        // 0.66 ms for one CTA per tile.)
         const bool relay = PAIR && half_id != 0u;
         const uint32_t me = (uint32_t)warp;
         const int q = warp & 3;
@@ -458,21 +468,14 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 ap.set((j0 + t) * PPS + sub0);
                 uint32_t sidx = plan_first_stage(plan, cta, nstages) + t;              // stage of the segment's K range handled next
                 uint32_t accumulate = 0u;                                        // 0 only for this issuer's first MMA of the segment
-                for (; ok && t < nstages; t += IST) {
+                // (the second CTA of a pair issues nothing: its copies and its unpack warps report to the first CTA's barriers)
+                for (; ok && !relay && t < nstages; t += IST) {
                     while (sidx >= nstages) sidx -= nstages;
                     const uint32_t cnt = seg.nkb - sidx * KS < (uint32_t)KS ? seg.nkb - sidx * KS : (uint32_t)KS;
                     sidx += IST;
                     if (!PROF_WAIT(1, ptx::mbar_wait_warp(b_full + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
                     PROF_COUNT(6)
                     PROF_TRACE(2, j0 + t);
-                    if constexpr (PAIR) {
-                        if (relay) {
-                            ptx::mbar_arrive_remote_elected(ptx::mapa(b_peer + 8 * rp.idx, 0u));
-                            rp.advance(IST);
-                            continue;
-                        }
-                        if (!PROF_WAIT(2, ptx::mbar_wait_warp(b_peer + 8 * rp.idx, rp.lap, abort_word, kErrStageFull))) { ok = false; break; }
-                    }
                     const uint64_t b_desc = b_desc0 + (uint64_t)(rp.idx * (Cfg::b_stride >> 4));
 #pragma unroll
                     for (uint32_t sub = sub0; sub < PPS; sub += (uint32_t)NI) {
@@ -725,7 +728,7 @@ fpx_gemm_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_consta
                 }
                 if (!ok) break;
                 {
-                    const uint32_t mine = Cfg::unified ? b_full : a_full, peers = Cfg::unified ? b_peer : a_peer;
+                    const uint32_t mine = Cfg::unified ? b_full : a_full, peers = Cfg::unified ? b_full : a_peer;
                     pending_bar = (PAIR && half_id != 0u) ? ptx::mapa(peers + 8 * slot, 0u) : mine + 8 * slot;
                 }
                 hand_over();

@@ -179,6 +179,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
         ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
         : "memory");
 }
+// The same copy issued by a CTA of a pair (cluster of two): the data lands in the issuing CTA's shared memory, the
+// transaction bytes are counted on `bar`, a shared::cluster address that may name a barrier of EITHER CTA of the pair
+// (no multicast: one destination).
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
+                                                 uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.cta_group::2.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
+        : "memory");
+}
 // 2-D tiled tensor copy global -> shared; x is the innermost coordinate.
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar,
                                             uint64_t policy) {
@@ -209,13 +220,16 @@ __device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
     return r;
 }
-// One lane of the (converged) warp arrives on a barrier of another CTA of the cluster (address from mapa).
+// One lane of the (converged) warp arrives on a barrier of another CTA of the cluster (address from mapa).  Without
+// the .release.cluster qualifiers: with them a warp spent ~1900 cycles per arrive (the cluster-scope release waits for
+// everything the thread has in flight), and what the arrive announces here - tensor-memory stores already waited for
+// with tcgen05.wait::st, an accumulator already read - is complete before it is issued.
 __device__ __forceinline__ void mbar_arrive_remote_elected(uint32_t cluster_addr) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
         "elect.sync _|p, 0xffffffff;\n\t"
-        "@p mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n\t"
+        "@p mbarrier.arrive.shared::cluster.b64 _, [%0];\n\t"
         "}\n" ::"r"(cluster_addr)
         : "memory");
 }
