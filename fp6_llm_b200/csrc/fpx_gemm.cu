@@ -906,7 +906,9 @@ __global__ void __launch_bounds__(32) gather_barrier_kernel(const __grid_constan
     __syncwarp();
     if (r == 0) *epoch_counter = epoch;
     if (r >= world) return;
-    __threadfence_system();
+    // The release is cumulative: this rank's stores into the peers' buffers were made by the grids that this kernel waited
+    // for above, so they are ordered before the flag at system scope by the release itself (a separate system-scope fence
+    // before it would cost a second round trip).
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.ptr[r] + rank), "r"(epoch) : "memory");
     const uint32_t* mine = flags.ptr[rank] + r;
     const unsigned long long t0 = ptx::global_timer_ns();
