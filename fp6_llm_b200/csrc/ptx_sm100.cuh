@@ -233,9 +233,6 @@ __device__ __forceinline__ void mbar_arrive_remote_elected(uint32_t cluster_addr
         "}\n" ::"r"(cluster_addr)
         : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
 
 // ------------------------------------------------------------------ tensor memory
 // Whole-warp calls.  `ncols` is a power of two >= 32; the base address is written to *smem_holder.
@@ -270,11 +267,6 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// The same for MMAs issued for a CTA pair: the barrier at this shared-memory offset arrives in both CTAs.
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(bar), "h"((uint16_t)3) : "memory");
-}
 // The same instructions for a role that a WHOLE warp executes, converged, with one elected lane issuing: addresses and
 // descriptors then stay warp-uniform, and a round of four MMAs and a commit costs the warp ~64 cycles where a branch
 // taken by one lane alone pays ~230 (and ~200 more for every barrier wait whose result it consumes).
@@ -289,6 +281,9 @@ __device__ __forceinline__ void mma_f16_ts_elect(uint32_t d_tmem, uint32_t a_tme
         "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The MMA issued by the first CTA of a pair for both: M = 256 (rows 0..127 from this CTA's tensor memory, 128..255 from
+// the peer's, at the same address), B's N rows split between the two CTAs' shared memories (same offset), each CTA's
+// accumulator holds its own 128 rows.
 __device__ __forceinline__ void mma_f16_ts_pair_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                       uint32_t accumulate) {
     asm volatile(
@@ -309,6 +304,7 @@ __device__ __forceinline__ void tc_commit_elect(uint32_t bar) {
         "}\n" ::"r"(bar)
         : "memory");
 }
+// The commit for MMAs issued for a CTA pair: the barrier at this shared-memory offset arrives in both CTAs.
 __device__ __forceinline__ void tc_commit_pair_elect(uint32_t bar) {
     asm volatile(
         "{\n\t"
@@ -329,19 +325,6 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// The same issued by the first CTA of a pair for both: M = 256 (rows 0..127 from this CTA's tensor memory, 128..255 from
-// the peer's, at the same address), B's N rows split between the two CTAs' shared memories (same offset), each CTA's
-// accumulator holds its own 128 rows.
-__device__ __forceinline__ void mma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
         "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
